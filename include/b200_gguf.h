@@ -35,6 +35,8 @@ extern "C" {
 #define B2_TYPE_Q4_K 12
 #define B2_TYPE_Q5_K 13
 #define B2_TYPE_Q6_K 14
+#define B2_TYPE_I32 26    /* integer tables of layer-list models */
+#define B2_TYPE_BF16 30   /* dense tensors of layer-list models (safetensors BF16) */
 
 typedef struct b2_engine b2_engine;
 
@@ -53,6 +55,7 @@ typedef struct b2_config {
 #define B2_FLAG_NO_GRAPH 1      /* launch kernels directly instead of replaying CUDA graphs */
 #define B2_FLAG_NO_PDL 2        /* no programmatic dependent launch between kernels */
 #define B2_FLAG_ACT8 4          /* single int8 activation plane (faster, ~0.5% noise) */
+#define B2_FLAG_F32 8           /* layer-list models: every product in true 32-bit (no tensor cores), f32 cache pages */
 
 typedef struct b2_sampling {
     float temperature;        /* <= 0: greedy */
@@ -129,6 +132,56 @@ int b2_forward_pending(b2_engine* e, int slot);
 /* Copy the slot's current logits [n_vocab] to the host (llama_get_logits). */
 int b2_get_logits(b2_engine* e, int slot, float* host_out);
 int b2_synchronize(b2_engine* e);
+
+/* ---- layer-list models: decoders given as a list of layers over dense bf16 / f32 tensors (no counterpart in the
+ *      reference, whose libllama only builds the graphs compiled into it). Each layer = one token mixer + an optional
+ *      feed-forward block, both followed by a layer norm AFTER the residual sum: x <- LN(residual_scale * x + f(x)).
+ *      Tensor names follow the Goponex files: embed, final.norm, head, l<i>.norm1/2, l<i>.mix.*, l<i>.mlp.*. ------------ */
+#define B2_MIX_WINDOW_SCAN 1     /* sliding-window attention with a kept prefix (values = raw keys) beside a selective
+                                    scan (Mamba); the two outputs are RMS-normed over the width and averaged */
+#define B2_MIX_MATRIX_MEMORY 2   /* mLSTM: per-head matrix memory with capped exponential gating */
+typedef struct b2_layer_desc {
+    int32_t mixer;            /* B2_MIX_* */
+    int32_t n_ff;             /* width of the squared-ReLU feed-forward block; 0 = the layer has none */
+    /* window attention */
+    int32_t n_head, n_head_kv, head_dim, rot_dims, window, keep_first, rope_orig_ctx, pad0_;
+    double attn_scale, rope_base, rope_factor /* <= 0: no frequency blending */, rope_fast, rope_slow;
+    /* selective scan */
+    int32_t conv_taps, dt_rank, d_inner, d_state;
+    /* matrix memory */
+    int32_t mm_heads, mm_dim, mm_vdim, pad_;
+    double gate_cap;
+} b2_layer_desc;
+typedef struct b2_layered_config {
+    int32_t n_layer, n_embd, n_vocab;
+    float norm_eps, residual_scale;
+    int32_t n_ctx;            /* max tokens per sequence */
+    int32_t max_seqs;         /* sequence slots = recurrent-state slots */
+    int32_t kv_block_tokens, kv_num_blocks;
+    int32_t max_step_tokens;  /* most tokens one b2_step call may bring */
+    int32_t device, flags;    /* B2_FLAG_F32 */
+} b2_layered_config;
+/* Then b2_upload_tensor for every tensor (BF16 / F32), b2_engine_finalize, b2_seq_set_blocks / b2_seq_begin (n_past must be
+ * 0: recurrent state cannot be rewound; it zeroes the slot's state) as for any engine. */
+int b2_engine_create_layered(const b2_layered_config* cfg, const b2_layer_desc* layers, b2_engine** out);
+
+/* One step over a ragged batch: entry i brings n_tokens[i] consecutive tokens (a prompt portion or one decoded token) of
+ * the sequence in slots[i], continuing from what earlier steps left in its pages and state; `host_tokens` holds all
+ * entries' tokens one after another. `want_rows` (indices into host_tokens) are the rows whose logits are copied to
+ * host_logits [n_want][n_vocab]. sample[i] != 0: sample from the logits of entry i's last token with the slot's sampler
+ * and return the token in host_sampled[i] (-1 elsewhere); those logits also stay in the slot's logit buffer. Any of
+ * want_rows / sample / host_sampled may be NULL. */
+#define B2_STEP_MAX_ENTRIES 64
+int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const int32_t* n_tokens, const int32_t* host_tokens,
+            const int32_t* want_rows, int n_want, float* host_logits, const int32_t* sample, int32_t* host_sampled);
+/* Debugging / parity: keep the residual stream after every layer of the next steps (on != 0), and read it back:
+ * host_out [n_layer][T][n_embd] for the T tokens of the last step. */
+int b2_step_trace(b2_engine* e, int on);
+int b2_step_trace_read(b2_engine* e, float* host_out, int n_layer, int T);
+/* Device time of the last `b2_step` by kernel kind (events around every launch when on != 0; slows the step down).
+ * kinds: 0 embed, 1 dense products, 2 attention, 3 scan, 4 matrix memory, 5 norms, 6 head. ms_out[8], launches_out[8]. */
+int b2_step_profile(b2_engine* e, int on);
+int b2_step_profile_read(b2_engine* e, float* ms_out, int32_t* launches_out);
 
 /* ---- measurement hooks (bench.py): CUDA events on the engine's own stream --------------- */
 int b2_timer_start(b2_engine* e);

@@ -1,0 +1,209 @@
+// Dense products for the layer-list models: Y[T][N] = epi(X[T][K] . W[N][K]^T + bias), weights bf16 or f32 as stored
+// in the file, activations f32 in memory. Three kernels:
+//   dense_rows_kernel   T <= 8 (decode steps): one warp per weight row, the row is streamed once for all tokens
+//   dense_mma_kernel    T > 8, bf16 weights: tensor cores (mma.sync m16n8k16 bf16, f32 accumulate), X rounded to bf16
+//   dense_fma_kernel    T > 8, exact mode (or f32 weights): 32-bit multiply-adds, nothing rounded
+// Every output element is one sum over k in a fixed order that depends only on (K, kernel), never on T or on the
+// other rows, so a token's result is the same whatever else shares the step. Arbitrary T, N, K (edges are guarded).
+// The llama graph's counterpart (quantised blocks, tcgen05) is gemm.cu / matvec.cu.
+#include "kernels.h"
+#include "layered.h"
+#include "ptx.cuh"
+#include "quant_blocks.cuh"
+
+namespace b2 {
+
+__device__ __forceinline__ float ld_w(const __nv_bfloat16* w, size_t i) { return __bfloat162float(w[i]); }
+__device__ __forceinline__ float ld_w(const float* w, size_t i) { return w[i]; }
+
+__device__ __forceinline__ float apply_epi(float v, const float* bias, int n, int epi) {
+    if (epi != EPI_NONE && bias) v += bias[n];
+    if (epi == EPI_BIAS_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+    return v;
+}
+
+// ---------------------------------------------------------------- few tokens: a warp per weight row
+constexpr int ROWS_MAX_T = 8;
+template <typename TW>
+__global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
+                                                         const float* __restrict__ bias, float* __restrict__ y, int ldy,
+                                                         int T, int N, int K, int epi) {
+    griddep_launch();
+    griddep_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const TW* row = w + (size_t)n * K;
+    float acc[ROWS_MAX_T];
+#pragma unroll
+    for (int t = 0; t < ROWS_MAX_T; t++) acc[t] = 0.f;
+    // lanes take k = lane, lane + 32, ...: neighbouring lanes read neighbouring weights
+    for (int k = lane; k < K; k += 32) {
+        const float wv = ld_w(row, k);
+#pragma unroll
+        for (int t = 0; t < ROWS_MAX_T; t++)
+            if (t < T) acc[t] = fmaf(x[(size_t)t * ldx + k], wv, acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < ROWS_MAX_T; t++) {
+        if (t < T) {
+            float v = warp_sum(acc[t]);
+            if (lane == 0) y[(size_t)t * ldy + n] = apply_epi(v, bias, n, epi);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- exact: 64 x 64 tile, 16-deep, 4 x 4 per thread
+template <typename TW>
+__global__ void __launch_bounds__(256) dense_fma_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
+                                                        const float* __restrict__ bias, float* __restrict__ y, int ldy,
+                                                        int T, int N, int K, int epi) {
+    griddep_launch();
+    griddep_wait();
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float xs[BK][BM + 4];
+    __shared__ float ws[BK][BN + 4];
+    const int t0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // thread tile: rows ty*4.., cols tx*4..
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += 256) {
+            const int r = i / BK, kk = i % BK;
+            const int t = t0 + r, k = k0 + kk;
+            xs[kk][r] = (t < T && k < K) ? x[(size_t)t * ldx + k] : 0.f;
+            const int n = n0 + r;
+            ws[kk][r] = (n < N && k < K) ? ld_w(w, (size_t)n * K + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = xs[kk][ty * 4 + i]; b[i] = ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) y[(size_t)t * ldy + n] = apply_epi(acc[i][j], bias, n, epi);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- tensor cores: 64 x 64 tile, 32-deep, 4 warps of 32 x 32
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
+                                                        const float* __restrict__ bias, float* __restrict__ y, int ldy,
+                                                        int T, int N, int K, int epi) {
+    griddep_launch();
+    griddep_wait();
+    constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;      // rows padded by 16 bytes: fragment reads hit 32 banks
+    __shared__ __align__(16) __nv_bfloat16 xs[BM][LD];
+    __shared__ __align__(16) __nv_bfloat16 ws[BN][LD];
+    const int t0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int g = lane >> 2, tq = lane & 3;
+    float acc[2][4][4] = {};
+    const bool w_vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        // X tile: f32 -> bf16 (round to nearest even), 64 x 32
+        for (int i = threadIdx.x; i < BM * BK / 2; i += 128) {
+            const int r = i / (BK / 2), kk = (i % (BK / 2)) * 2;
+            const int t = t0 + r, k = k0 + kk;
+            float v0 = 0.f, v1 = 0.f;
+            if (t < T) {
+                if (k < K) v0 = x[(size_t)t * ldx + k];
+                if (k + 1 < K) v1 = x[(size_t)t * ldx + k + 1];
+            }
+            *reinterpret_cast<__nv_bfloat162*>(&xs[r][kk]) = __floats2bfloat162_rn(v0, v1);
+        }
+        // W tile: 64 rows x 32 bf16
+        if (w_vec) {
+            for (int i = threadIdx.x; i < BN * BK / 8; i += 128) {
+                const int r = i / (BK / 8), kk = (i % (BK / 8)) * 8;
+                const int n = n0 + r, k = k0 + kk;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (n < N && k < K) v = *reinterpret_cast<const uint4*>(w + (size_t)n * K + k);
+                *reinterpret_cast<uint4*>(&ws[r][kk]) = v;
+            }
+        } else {
+            for (int i = threadIdx.x; i < BN * BK; i += 128) {
+                const int r = i / BK, kk = i % BK;
+                const int n = n0 + r, k = k0 + kk;
+                ws[r][kk] = (n < N && k < K) ? w[(size_t)n * K + k] : __float2bfloat16(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < BK; ks += 16) {
+            uint32_t af[2][4], bf[4][2];
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                const int r = wm + mi * 16 + g;
+                af[mi][0] = *reinterpret_cast<const uint32_t*>(&xs[r][ks + 2 * tq]);
+                af[mi][1] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][ks + 2 * tq]);
+                af[mi][2] = *reinterpret_cast<const uint32_t*>(&xs[r][ks + 2 * tq + 8]);
+                af[mi][3] = *reinterpret_cast<const uint32_t*>(&xs[r + 8][ks + 2 * tq + 8]);
+            }
+#pragma unroll
+            for (int ni = 0; ni < 4; ni++) {
+                const int c = wn + ni * 8 + g;
+                bf[ni][0] = *reinterpret_cast<const uint32_t*>(&ws[c][ks + 2 * tq]);
+                bf[ni][1] = *reinterpret_cast<const uint32_t*>(&ws[c][ks + 2 * tq + 8]);
+            }
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 4; ni++) mma_bf16_16816(acc[mi][ni], af[mi], bf[ni]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int t = t0 + wm + mi * 16 + g + (e >> 1) * 8;
+                const int n = n0 + wn + ni * 8 + 2 * tq + (e & 1);
+                if (t < T && n < N) y[(size_t)t * ldy + n] = apply_epi(acc[mi][ni][e], bias, n, epi);
+            }
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args&&... args) {
+    return launch_chain(k, grid, block, 0, s, std::forward<Args>(args)...);
+}
+
+cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
+    if (a.T <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+    if (a.w_type != T_BF16 && a.w_type != T_F32) return cudaErrorInvalidValue;
+    const bool wb = a.w_type == T_BF16;
+    if (a.T <= ROWS_MAX_T) {
+        dim3 grid((a.N + 7) / 8), block(256);
+        if (wb) return launch_pdl(dense_rows_kernel<__nv_bfloat16>, grid, block, s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+        return launch_pdl(dense_rows_kernel<float>, grid, block, s, a.x, a.ldx, (const float*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    }
+    dim3 grid((a.N + 63) / 64, (a.T + 63) / 64);
+    if (wb && !a.exact)
+        return launch_pdl(dense_mma_kernel, grid, dim3(128), s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    if (wb) return launch_pdl(dense_fma_kernel<__nv_bfloat16>, grid, dim3(256), s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    return launch_pdl(dense_fma_kernel<float>, grid, dim3(256), s, a.x, a.ldx, (const float*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+}
+
+}  // namespace b2

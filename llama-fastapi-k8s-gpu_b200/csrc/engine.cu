@@ -3,8 +3,8 @@
 // per-slot activation buffers and the captured CUDA graphs of one decode / prefill step.
 // Stands in for libllama's llama_model + llama_context behind llama-cpp-python's Llama object
 // (/root/reference/api.py:24-28,55-63).
-#include "../../include/b200_gguf.h"
-#include "kernels.h"
+#include "engine_state.h"
+#include "layered.h"
 #include "ptx.cuh"
 #include "quant_blocks.cuh"
 
@@ -19,19 +19,12 @@
 #include <unordered_map>
 #include <vector>
 
-using namespace b2;
-
 static thread_local std::string g_err;
-static int fail(int code, const std::string& msg) { g_err = msg; return code; }
-#define CK(call)                                                                                   \
-    do {                                                                                           \
-        cudaError_t _e = (call);                                                                   \
-        if (_e != cudaSuccess)                                                                     \
-            return fail(B2_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_e));         \
-    } while (0)
+int b2_fail(int code, const std::string& msg) { g_err = msg; return code; }
+static int fail(int code, const std::string& msg) { return b2_fail(code, msg); }
 
 // kernel watchdogs (ptx.cuh mbar_wait) report through a host-mapped word; call after a sync
-static int check_kernel_error() {
+int b2_check_kernel_error() {
     unsigned int* w = kernel_error_word();
     if (w && *w) {
         unsigned int c = w[0];
@@ -43,87 +36,6 @@ static int check_kernel_error() {
     }
     return B2_OK;
 }
-
-struct DevTensor {
-    uint8_t* ptr = nullptr;
-    int type = -1;
-    int64_t ne0 = 0, ne1 = 0, nbytes = 0;
-};
-
-struct Layer {
-    DevTensor attn_norm, wq, wk, wv, wo, ffn_norm, wgate, wup, wdown;
-    MvParams p_qkv, p_o, p_gu, p_down;
-    MvParams p_gate, p_up;         // un-fused pair when ffn_gate and ffn_up have different quant types
-    bool gu_fused = true;
-};
-
-struct Slot {
-    float *x = nullptr, *q = nullptr, *att = nullptr, *h = nullptr, *hg = nullptr, *logits = nullptr;
-    float* tp_part = nullptr;      // tensor parallelism: this rank's partial sum of attn_output / ffn_down (rank 0: + the residual)
-    int* ints = nullptr;           // [0]=token [1]=pos [2]=out_token [3]=step [4]=cursor [5]=pos_base
-    int* block_table = nullptr;
-    int* prompt = nullptr;         // [n_ctx]
-    int* ring = nullptr;           // [n_ctx + 1] sampled token by position
-    SamplerState* sst = nullptr;
-    SampleParams* sp = nullptr;
-    double* uniforms = nullptr;    // [8192]
-    cudaGraphExec_t g_decode = nullptr, g_pre_step = nullptr, g_pre_last = nullptr, g_fwd = nullptr;
-    int n_decode_nodes = 0, n_pre_step_nodes = 0, n_pre_last_nodes = 0, n_fwd_nodes = 0;
-    const float* logits_view = nullptr;   // where the latest logits of this slot are (own buffer, or a row of the batch output)
-    int n_past = 0;                // host mirror of ints[1]
-    int n_sampled = 0;             // host mirror of ints[3]
-};
-
-struct b2_engine {
-    b2_config cfg;
-    cudaStream_t stream = nullptr;
-    std::unordered_map<std::string, DevTensor> tensors;
-    std::vector<Layer> layers;
-    DevTensor tok_embd, out_norm, output;
-    MvParams p_head;
-    __half *k_pool = nullptr, *v_pool = nullptr;
-    size_t layer_kv_elems = 0;
-    float* rope_freq = nullptr;
-    float* attn_scratch = nullptr;
-    unsigned* attn_counters = nullptr;
-    int n_splits = 1, max_blocks = 0, n_ctas = 148;
-    std::vector<Slot> slots;
-    int32_t* pinned = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    int64_t launches = 0, weight_bytes = 0, kv_bytes = 0;
-    bool use_graph = true, use_pdl = true, act2 = true, finalized = false, chain_pdl = true;
-    int batch_attn_splits = 0;     // B2_BATCH_ATTN_SPLITS (tuning), read once at create
-    int attn_early = 1;            // B2_ATTN_EARLY=0 (tuning): attention requests nothing before its dependency wait
-    // tensor parallelism (b2_engine_tp_init): this engine holds 1 / tp_world of the heads, FFN rows and vocabulary rows
-    void* tp_comm = nullptr;
-    int tp_rank = 0, tp_world = 1;
-    // all-reduce over peer memory (tp.cu): [2][n_embd] partial sums + flags + sequence number in one IPC-shared allocation
-    float* tp_shared = nullptr;
-    void* tp_peer[TP_MAX_WORLD] = {};
-    bool tp_p2p = false;
-    TpArParams tp_ar[2] = {};
-    unsigned long long* tl = nullptr;   // B2_TIMELINE=1: 4 time stamps per kernel of a decode step (debugging aid)
-    int tl_n = 0;                  // kernels recorded by the last forward_launches
-    // prompt (GEMM) workspace, allocated on the first long prompt: PF_T tokens per chunk
-    float *pf_x = nullptr, *pf_part = nullptr;     // residual stream [PF_T][n_embd]; K-split partial sums of the last GEMM
-    size_t pf_part_floats = 0;
-    __half *pf_xn = nullptr, *pf_qh = nullptr, *pf_att = nullptr, *pf_h = nullptr;
-    int n_sms = 148;
-    // batched decode (several sequences per step through the GEMM path)
-    SlotDev* slot_tab = nullptr;   // device table, one entry per slot
-    float *bd_q = nullptr, *bd_att = nullptr, *bd_scratch = nullptr;
-    unsigned* bd_counters = nullptr;
-    int* bd_out = nullptr;
-    int attn_mma = -1;             // tensor-core flash-decode: -1 = batched steps only; 0 never; 1 always
-    int batch_min = 3;             // fewer sequences than this step one after another through the mat-vec path (measured: 3 slots 4.1 vs 6.3 ms)
-    bool gemm_ok = false;          // every layer matrix is a block format the GEMM reads
-    int prefill_min = 8;           // prompts chunks shorter than this go token by token through the mat-vec path
-    // GEMM launch plans (tile split, K splits, tensor maps) are built once per (first weight matrix, token count) and reused:
-    // re-planning -- cuTensorMapEncodeTiled and a handful of getenv per call -- for each of the 129 GEMMs of every batched
-    // step cost more host time than the step takes on the GPU
-    std::unordered_map<uint64_t, GemmParams> gemm_plans;
-    std::mutex mu;
-};
 
 // ------------------------------------------------------------------------------------------
 // small device helpers
@@ -278,6 +190,7 @@ extern "C" int b2_engine_destroy(b2_engine* e) {
     if (!e) return B2_OK;
     cudaSetDevice(e->cfg.device);
     if (e->stream) cudaStreamSynchronize(e->stream);
+    layered_destroy(e);
     for (auto& kv : e->tensors) cudaFree(kv.second.ptr);
     for (auto& s : e->slots) {
         free_slot_graphs(s);
@@ -332,7 +245,7 @@ static int get_tensor(b2_engine* e, const std::string& name, int64_t ne0, int64_
                                     std::to_string(t.ne1) + "], expected [" + std::to_string(ne0) + "," +
                                     std::to_string(ne1) + "]");
     if (!quant_ok && t.type != T_F32) return fail(B2_ERR_UNSUPPORTED, "tensor " + name + " must be F32");
-    if (quant_ok && (t.type == T_F32 || t.type == T_F16))
+    if (quant_ok && block_elems(t.type) == 1)
         return fail(B2_ERR_UNSUPPORTED, "tensor " + name + ": F32/F16 weight matrices are not supported by the mat-vec yet");
     out = t;
     return B2_OK;
@@ -360,6 +273,7 @@ extern "C" int b2_tp_unique_id(void* out128) {
 
 extern "C" int b2_engine_tp_init(b2_engine* e, int rank, int world, const void* id128) {
     if (!e || !id128) return fail(B2_ERR_ARG, "null argument");
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     if (e->finalized) return fail(B2_ERR_STATE, "b2_engine_tp_init must come before b2_engine_finalize");
     if (world < 2 || rank < 0 || rank >= world) return fail(B2_ERR_ARG, "bad rank / world");
     std::lock_guard<std::mutex> lk(e->mu);
@@ -440,6 +354,7 @@ static bool gemm_type_ok(int t) { return block_elems(t) != 1 && block_bytes(t) !
 extern "C" int b2_engine_finalize(b2_engine* e) {
     if (!e) return fail(B2_ERR_ARG, "null engine");
     std::lock_guard<std::mutex> lk(e->mu);
+    if (e->layered) return layered_finalize(e);
     const b2_config& c = e->cfg;
     int rc;
     int qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim;
@@ -723,6 +638,10 @@ extern "C" int b2_seq_begin(b2_engine* e, int slot, int n_past, const int32_t* h
         return fail(B2_ERR_UNSUPPORTED, "top_k must be in 1..1024 on the device sampler");
     CK(cudaSetDevice(e->cfg.device));
     Slot& s = e->slots[slot];
+    if (e->layered) {      // recurrent state cannot be cut back to a prefix: a sequence always starts from nothing
+        if (n_past != 0) return fail(B2_ERR_UNSUPPORTED, "layer-list models start every sequence at position 0 (no prefix reuse)");
+        if ((rc = layered_seq_reset(e, slot))) return rc;
+    }
     SamplerState h = {};
     for (int i = 0; i < n_hist; i++) h.history[i] = hist[i];
     h.n_hist = n_hist;
@@ -835,6 +754,7 @@ static int prefill_chunk(b2_engine* e, Slot& s, const int* tokens, int T, int po
 
 extern "C" int b2_prefill(b2_engine* e, int slot, const int32_t* tokens, int n) {
     int rc = check_slot(e, slot); if (rc) return rc;
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     std::lock_guard<std::mutex> lk(e->mu);
     Slot& s = e->slots[slot];
     if (n <= 0) return fail(B2_ERR_ARG, "empty prompt chunk");
@@ -868,27 +788,34 @@ extern "C" int b2_prefill(b2_engine* e, int slot, const int32_t* tokens, int n) 
         }
     }
     CK(cudaStreamSynchronize(e->stream));
-    if ((rc = check_kernel_error())) return rc;
+    if ((rc = b2_check_kernel_error())) return rc;
     s.n_past += n;     // device pos stays at the last token; b2_sample / set_token move it on
     return B2_OK;
 }
 
 __global__ void set_ints_kernel(int* ints, int tok, int pos) { if (tok >= 0) ints[0] = tok; ints[1] = pos; }
 
-extern "C" int b2_sample(b2_engine* e, int slot, int32_t* out) {
-    int rc = check_slot(e, slot); if (rc) return rc;
-    std::lock_guard<std::mutex> lk(e->mu);
-    Slot& s = e->slots[slot];
-    CK(cudaSetDevice(e->cfg.device));
+// enqueue: sample from the slot's logit buffer (the token at position n_past - 1 was the last one evaluated); the token
+// lands in e->pinned[pinned_index] once the stream has been synchronised
+int b2_sample_enqueue(b2_engine* e, Slot& s, int pinned_index) {
     // sampler bumps pos: make it point at the last evaluated token first
     set_ints_kernel<<<1, 1, 0, e->stream>>>(s.ints, -1, s.n_past - 1);
     CK(sample_launch(s.logits, e->cfg.n_vocab, s.sp, s.sst, s.uniforms, s.ints + 3, s.ints + 2, s.ints + 0,
                      s.ints + 1, s.ring, e->cfg.n_ctx + 1, e->stream, false));
     e->launches += 2;
-    CK(cudaMemcpyAsync(e->pinned, s.ints + 2, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaMemcpyAsync(e->pinned + pinned_index, s.ints + 2, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    s.n_sampled += 1;
+    return B2_OK;
+}
+
+extern "C" int b2_sample(b2_engine* e, int slot, int32_t* out) {
+    int rc = check_slot(e, slot); if (rc) return rc;
+    std::lock_guard<std::mutex> lk(e->mu);
+    Slot& s = e->slots[slot];
+    CK(cudaSetDevice(e->cfg.device));
+    if ((rc = b2_sample_enqueue(e, s, 0))) return rc;
     CK(cudaStreamSynchronize(e->stream));
     if (out) *out = e->pinned[0];
-    s.n_sampled += 1;
     return B2_OK;
 }
 
@@ -975,6 +902,7 @@ extern "C" int b2_decode(b2_engine* e, const int32_t* slots, int n, int32_t* out
     if (!e->finalized) return fail(B2_ERR_STATE, "engine not finalized");
     std::lock_guard<std::mutex> lk(e->mu);
     if (n > (int)e->slots.size()) return fail(B2_ERR_ARG, "more slots than max_seqs");
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     CK(cudaSetDevice(e->cfg.device));
     for (int i = 0; i < n; i++) {
         if (slots[i] < 0 || slots[i] >= (int)e->slots.size()) return fail(B2_ERR_ARG, "slot out of range");
@@ -1007,13 +935,14 @@ extern "C" int b2_decode(b2_engine* e, const int32_t* slots, int n, int32_t* out
         }
     }
     CK(cudaStreamSynchronize(e->stream));
-    { int rc2 = check_kernel_error(); if (rc2) return rc2; }
+    { int rc2 = b2_check_kernel_error(); if (rc2) return rc2; }
     if (out) for (int i = 0; i < n; i++) out[i] = e->pinned[i];
     return B2_OK;
 }
 
 extern "C" int b2_decode_n(b2_engine* e, int slot, int n, int32_t* out) {
     int rc = check_slot(e, slot); if (rc) return rc;
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     std::lock_guard<std::mutex> lk(e->mu);
     Slot& s = e->slots[slot];
     if (n <= 0) return fail(B2_ERR_ARG, "n must be positive");
@@ -1055,7 +984,7 @@ extern "C" int b2_decode_n(b2_engine* e, int slot, int n, int32_t* out) {
     // step i forwards the token at position n_past+i and its sample lands at ring[n_past+i+1]
     CK(cudaMemcpyAsync(e->pinned, s.ring + s.n_past + 1, sizeof(int) * n, cudaMemcpyDeviceToHost, e->stream));
     CK(cudaStreamSynchronize(e->stream));
-    if ((rc = check_kernel_error())) return rc;
+    if ((rc = b2_check_kernel_error())) return rc;
     if (out) memcpy(out, e->pinned, sizeof(int) * n);
     s.n_past += n;
     s.n_sampled += n;
@@ -1064,6 +993,7 @@ extern "C" int b2_decode_n(b2_engine* e, int slot, int n, int32_t* out) {
 
 extern "C" int b2_seq_rewind(b2_engine* e, int slot, int n_keep, int32_t pending, const int32_t* hist, int n_hist) {
     int rc = check_slot(e, slot); if (rc) return rc;
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     std::lock_guard<std::mutex> lk(e->mu);
     Slot& s = e->slots[slot];
     if (n_keep < 0 || n_keep > s.n_past) return fail(B2_ERR_ARG, "n_keep out of range");
@@ -1097,6 +1027,7 @@ extern "C" int b2_seq_set_token(b2_engine* e, int slot, int32_t token) {
 
 extern "C" int b2_forward_pending(b2_engine* e, int slot) {
     int rc = check_slot(e, slot); if (rc) return rc;
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     std::lock_guard<std::mutex> lk(e->mu);
     Slot& s = e->slots[slot];
     if (s.n_past + 1 > e->cfg.n_ctx) return fail(B2_ERR_ARG, "context window full");
@@ -1106,7 +1037,7 @@ extern "C" int b2_forward_pending(b2_engine* e, int slot) {
     rc = run_step(e, s, GK_FWD);
     if (rc) return rc;
     CK(cudaStreamSynchronize(e->stream));
-    if ((rc = check_kernel_error())) return rc;
+    if ((rc = b2_check_kernel_error())) return rc;
     s.n_past += 1;
     return B2_OK;
 }
@@ -1163,6 +1094,7 @@ static int64_t seg_bytes(const MvParams& p) {
 
 extern "C" int b2_profile_decode_step(b2_engine* e, int slot, float* ms, int32_t* nl, int64_t* bytes) {
     int rc = check_slot(e, slot); if (rc) return rc;
+    if (e->layered) return fail(B2_ERR_UNSUPPORTED, "this entry point drives the llama graph; layer-list engines are stepped with b2_step");
     std::lock_guard<std::mutex> lk(e->mu);
     Slot& s = e->slots[slot];
     if (s.n_past + 1 > e->cfg.n_ctx) return fail(B2_ERR_ARG, "context window full");
@@ -1244,7 +1176,7 @@ static int op_matvec_common(int device, MvParams& p, const void* w0, const void*
     if ((rc = mv_plan(p, n_ctas))) return fail(B2_ERR_UNSUPPORTED, "mat-vec plan failed");     // again, now that the weights have their addresses (tensor maps)
     CK(mv_launch(p, n_ctas, 0, planes != 1, false));
     CK(cudaDeviceSynchronize());
-    { int rc2 = check_kernel_error(); if (rc2) return rc2; }
+    { int rc2 = b2_check_kernel_error(); if (rc2) return rc2; }
 
     CK(cudaMemcpy(y, dy.p, (size_t)n_rows * 4, cudaMemcpyDeviceToHost));
     return B2_OK;
@@ -1336,7 +1268,7 @@ extern "C" int b2_bench_matvec(int device, int mode, int type, int n_rows, int K
     }
     CK(cudaEventElapsedTime(&ms, e0, e1));
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaStreamDestroy(st);
-    if (int rc2 = check_kernel_error()) return rc2;
+    if (int rc2 = b2_check_kernel_error()) return rc2;
     *us_out = ms * 1000.f / (float)iters;
     return B2_OK;
 }
@@ -1384,7 +1316,7 @@ extern "C" int b2_op_gemm(int device, int type, const void* w, int n_rows, int K
                                                                y_in ? dyin.as<float>() : nullptr, (long)out_n, dy.as<float>());
     CK(cudaGetLastError());
     CK(cudaDeviceSynchronize());
-    if (int rc = check_kernel_error()) return rc;
+    if (int rc = b2_check_kernel_error()) return rc;
     CK(cudaMemcpy(y, dy.p, out_n * 4, cudaMemcpyDeviceToHost));
     if (p.dbg) {      // debugging aid: pipeline timeline of CTA 0, cycles relative to the first record
         std::vector<long long> t(64 * 8);
@@ -1455,7 +1387,7 @@ extern "C" int b2_op_attention_decode(int device, const float* q, const uint16_t
     if (use_mma) { CK(attn_mma_init()); CK(attn_decode_mma_launch(a, nullptr, nullptr, 0, false)); }
     else CK(attn_decode_launch(a, 0, false));
     CK(cudaDeviceSynchronize());
-    { int rc2 = check_kernel_error(); if (rc2) return rc2; }
+    { int rc2 = b2_check_kernel_error(); if (rc2) return rc2; }
     CK(cudaMemcpy(out, dout.p, (size_t)n_head * hd * 4, cudaMemcpyDeviceToHost));
     return B2_OK;
 }

@@ -1,0 +1,406 @@
+// Token mixers and norms of the layer-list models, over a ragged step (layered.h): post-sum layer norm with RMS-normed
+// branches, sliding-window attention with a kept prefix over the paged cache (query/key norm, partial interleaved
+// rotary with blended frequencies, values = un-normalised keys), selective scan (causal depthwise convolution +
+// diagonal state recurrence), and the mLSTM matrix memory. Softmax, norms, gates, decays and all recurrent state are
+// 32-bit; only the cache pages may be bf16. Every recurrence walks a segment's tokens in order from the state its
+// slot holds, so a sequence cut into portions gives the same numbers as the whole.
+#include "kernels.h"
+#include "layered.h"
+#include "ptx.cuh"
+#include "quant_blocks.cuh"
+
+namespace b2 {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {      // all threads get the sum; red: >= 33 floats
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 0.f ? z + log1pf(expf(-z)) : log1pf(expf(z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) { return -softplus_f(-z); }
+
+// ---------------------------------------------------------------- embedding, gather
+template <typename TW>
+__global__ void embed_ragged_kernel(const TW* __restrict__ table, int W, const int* __restrict__ tok, float* __restrict__ x) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const TW* row = table + (size_t)tok[t] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        if constexpr (sizeof(TW) == 2) x[(size_t)t * W + i] = __bfloat162float(row[i]);
+        else x[(size_t)t * W + i] = row[i];
+    }
+}
+cudaError_t embed_ragged_launch(const void* table, int w_type, int W, const int* tok_id, int T, float* x, cudaStream_t s) {
+    if (w_type == T_BF16) return launch_chain(embed_ragged_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, W, tok_id, x);
+    if (w_type == T_F32) return launch_chain(embed_ragged_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, W, tok_id, x);
+    return cudaErrorInvalidValue;
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ x, int W, const int* __restrict__ rows, float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    const float* src = x + (size_t)rows[blockIdx.x] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[(size_t)blockIdx.x * W + i] = src[i];
+}
+cudaError_t gather_rows_launch(const float* x, int W, const int* rows, int n, float* y, cudaStream_t s) {
+    return launch_chain(gather_rows_kernel, dim3(n), dim3(128), 0, s, x, W, rows, y);
+}
+
+// ---------------------------------------------------------------- norms
+// one CTA per token; the row lives in shared memory between the passes (mean, then squared deviations)
+__global__ void __launch_bounds__(256) postsum_norm_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ wa,
+                                                           const float* __restrict__ b, const float* __restrict__ wb,
+                                                           const float* __restrict__ w, float alpha, float eps, int W) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * W;
+    float ra = 1.f, rb = 1.f;
+    if (b) {
+        float sa = 0.f, sb = 0.f;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) { const float u = a[base + i], v = b[base + i]; sa += u * u; sb += v * v; }
+        sa = block_sum(sa, red); sb = block_sum(sb, red);
+        ra = 1.f / sqrtf(sa / (float)W + eps); rb = 1.f / sqrtf(sb / (float)W + eps);
+    }
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float yv = b ? 0.5f * (a[base + i] * ra * wa[i] + b[base + i] * rb * wb[i]) : (a ? a[base + i] : 0.f);
+        const float v = alpha * x[base + i] + yv;
+        row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, red) / (float)W;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dlt = row[i] - mean; sq += dlt * dlt; }
+    const float rstd = 1.f / sqrtf(block_sum(sq, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) x[base + i] = (row[i] - mean) * rstd * w[i];
+}
+cudaError_t postsum_norm_launch(float* x, const float* a, const float* wa, const float* b, const float* wb, const float* w,
+                                float alpha, float eps, int W, int T, cudaStream_t s) {
+    return launch_chain(postsum_norm_kernel, dim3(T), dim3(256), (size_t)W * 4, s, x, a, wa, b, wb, w, alpha, eps, W);
+}
+
+__global__ void __launch_bounds__(256) layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int W,
+                                                         float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * W;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) sum += x[base + i];
+    const float mean = block_sum(sum, red) / (float)W;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float dlt = x[base + i] - mean; sq += dlt * dlt; }
+    const float rstd = 1.f / sqrtf(block_sum(sq, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[base + i] = (x[base + i] - mean) * rstd * w[i];
+}
+cudaError_t layer_norm_launch(const float* x, const float* w, float eps, int W, int T, float* y, cudaStream_t s) {
+    return launch_chain(layer_norm_kernel, dim3(T), dim3(256), 0, s, x, w, eps, W, y);
+}
+
+// ---------------------------------------------------------------- window attention
+__device__ __forceinline__ void cache_store(void* pool, int f32, size_t i, float v) {
+    if (f32) reinterpret_cast<float*>(pool)[i] = v;
+    else reinterpret_cast<__nv_bfloat16*>(pool)[i] = __float2bfloat16(v);
+}
+__device__ __forceinline__ float cache_load(const void* pool, int f32, size_t i) {
+    return f32 ? reinterpret_cast<const float*>(pool)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(pool)[i]);
+}
+
+// grid (T, H + G), one warp: head slots [0, H) are queries, [H, H + G) are key/value heads
+__global__ void __launch_bounds__(32) window_attn_store_kernel(WindowAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x, hs = blockIdx.y, lane = threadIdx.x;
+    const bool is_q = hs < a.H;
+    const int head = is_q ? hs : hs - a.H;
+    const float* src = a.proj + (size_t)t * a.ldp + (is_q ? a.q_off : a.k_off) + head * a.d;
+    const float* nw = is_q ? a.q_norm_w : a.k_norm_w;
+    const int pos = r.tok_pos[t];
+    float ss = 0.f;
+    for (int i = lane; i < a.d; i += 32) { const float v = src[i]; ss += v * v; }
+    const float rinv = 1.f / sqrtf(warp_sum(ss) / (float)a.d + a.eps);
+    size_t dst = 0;
+    if (!is_q) {
+        const int slot = r.seg_slot[r.tok_seg[t]];
+        const int page = a.block_tables[slot][pos / a.block_tokens];
+        dst = (((size_t)page * a.G + head) * a.block_tokens + pos % a.block_tokens) * a.d;
+    }
+    float* qdst = a.q_rot + (size_t)t * a.H * a.d + (size_t)head * a.d;
+    // pairs (2i, 2i+1): rotated inside the first rot_dims entries, passed through after them
+    for (int p = lane; 2 * p < a.d; p += 32) {
+        const int i0 = 2 * p, i1 = 2 * p + 1;
+        const float r0 = src[i0], r1 = i1 < a.d ? src[i1] : 0.f;
+        float u = r0 * rinv * nw[i0], v = i1 < a.d ? r1 * rinv * nw[i1] : 0.f;
+        if (i1 < a.rot.rot_dims) {
+            const size_t ti = (size_t)pos * (a.rot.rot_dims / 2) + p;
+            const float sn = a.rot.sin[ti], cs = a.rot.cos[ti];
+            const float u2 = u * cs - v * sn, v2 = v * cs + u * sn;
+            u = u2; v = v2;
+        }
+        if (is_q) {
+            qdst[i0] = u;
+            if (i1 < a.d) qdst[i1] = v;
+        } else {
+            cache_store(a.k_pool, a.cache_f32, dst + i0, u);
+            cache_store(a.v_pool, a.cache_f32, dst + i0, r0);
+            if (i1 < a.d) { cache_store(a.k_pool, a.cache_f32, dst + i1, v); cache_store(a.v_pool, a.cache_f32, dst + i1, r1); }
+        }
+    }
+}
+cudaError_t window_attn_store_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
+    return launch_chain(window_attn_store_kernel, dim3(r.T, a.H + a.G), dim3(32), 0, s, a, r);
+}
+
+// grid (T, H), 4 warps: warp w takes visible keys w, w + 4, ...; a lane holds entries lane, lane + 32, ... of the head
+constexpr int ATT_WARPS = 4, ATT_MAXE = 8;     // head size <= 256
+__global__ void __launch_bounds__(ATT_WARPS * 32) window_attn_kernel(WindowAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
+    __shared__ float sm_o[ATT_WARPS][ATT_MAXE * 32];
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = r.tok_pos[t];
+    const int slot = r.seg_slot[r.tok_seg[t]];
+    const int* table = a.block_tables[slot];
+    const int g = h / (a.H / a.G);
+    const float* q = a.q_rot + (size_t)t * a.H * a.d + (size_t)h * a.d;
+    float qr[ATT_MAXE], acc[ATT_MAXE];
+#pragma unroll
+    for (int e = 0; e < ATT_MAXE; e++) { const int i = lane + 32 * e; qr[e] = i < a.d ? q[i] * a.scale : 0.f; acc[e] = 0.f; }
+    // visible: the kept prefix [0, n_keep) and the window [lo, pos]
+    const int lo = max(0, pos - a.window + 1);
+    const int n_keep = min(a.keep_first, lo);
+    const int n_vis = n_keep + (pos - lo + 1);
+    float m = -INFINITY, l = 0.f;
+    for (int i = warp; i < n_vis; i += ATT_WARPS) {
+        const int j = i < n_keep ? i : lo + (i - n_keep);
+        const size_t base = (((size_t)table[j / a.block_tokens] * a.G + g) * a.block_tokens + j % a.block_tokens) * a.d;
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < ATT_MAXE; e++) { const int d = lane + 32 * e; if (d < a.d) dot = fmaf(qr[e], cache_load(a.k_pool, a.cache_f32, base + d), dot); }
+        const float sc = warp_sum(dot);
+        const float m_new = fmaxf(m, sc);
+        const float corr = expf(m - m_new), p = expf(sc - m_new);
+        l = l * corr + p;
+#pragma unroll
+        for (int e = 0; e < ATT_MAXE; e++) { const int d = lane + 32 * e; if (d < a.d) acc[e] = fmaf(p, cache_load(a.v_pool, a.cache_f32, base + d), acc[e] * corr); }
+        m = m_new;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < ATT_MAXE; e++) sm_o[warp][lane + 32 * e] = acc[e];
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w2 = 0; w2 < ATT_WARPS; w2++) M = fmaxf(M, sm_m[w2]);
+    float L = 0.f;
+    for (int w2 = 0; w2 < ATT_WARPS; w2++) if (sm_m[w2] > -INFINITY) L += sm_l[w2] * expf(sm_m[w2] - M);
+    for (int d = threadIdx.x; d < a.d; d += blockDim.x) {
+        float o = 0.f;
+        for (int w2 = 0; w2 < ATT_WARPS; w2++) if (sm_m[w2] > -INFINITY) o += sm_o[w2][d] * expf(sm_m[w2] - M);
+        a.out[(size_t)t * a.H * a.d + (size_t)h * a.d + d] = o / L;
+    }
+}
+cudaError_t window_attn_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
+    if (a.d > ATT_MAXE * 32) return cudaErrorInvalidValue;
+    return launch_chain(window_attn_kernel, dim3(r.T, a.H), dim3(ATT_WARPS * 32), 0, s, a, r);
+}
+
+// ---------------------------------------------------------------- selective scan
+// xc[t][c] = silu(bias[c] + sum_j w[c][j] * in[t - (taps-1) + j][c]); inputs before the segment come from the slot's state
+__global__ void __launch_bounds__(256) scan_conv_kernel(ScanArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int seg = r.tok_seg[t], slot = r.seg_slot[seg], i = t - r.seg_start[seg];
+    const int hist = a.taps - 1;
+    for (int c = threadIdx.x; c < a.inner; c += blockDim.x) {
+        float acc = a.conv_b[c];
+        for (int j = 0; j < a.taps; j++) {
+            const int srci = i - hist + j;
+            const float v = srci >= 0 ? a.proj[(size_t)(t - i + srci) * a.ldp + a.x_off + c]
+                                      : a.conv_state[((size_t)slot * a.inner + c) * hist + (hist + srci)];
+            acc = fmaf(a.conv_w[(size_t)c * a.taps + j], v, acc);
+        }
+        a.xc[(size_t)t * a.inner + c] = silu_f(acc);
+    }
+}
+cudaError_t scan_conv_launch(const ScanArgs& a, const RaggedDev& r, cudaStream_t s) {
+    return launch_chain(scan_conv_kernel, dim3(r.T), dim3(256), 0, s, a, r);
+}
+
+// grid (n_seg, inner / 8): a warp per channel, lanes over the states (SCAN_MAXS per lane)
+constexpr int SCAN_MAXS = 8;       // state size <= 256
+__global__ void __launch_bounds__(256) scan_recurrence_kernel(ScanArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    const int seg = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.y * 8 + warp;
+    if (c >= a.inner) return;
+    const int slot = r.seg_slot[seg], start = r.seg_start[seg], len = r.seg_len[seg];
+    const int hist = a.taps - 1;
+    // the convolution's memory moves on: the last taps-1 inputs of the sequence (read before written: index k + len > k)
+    if (lane == 0) {
+        float* st = a.conv_state + ((size_t)slot * a.inner + c) * hist;
+        for (int k = 0; k < hist; k++) {
+            const int srci = len + k - hist;
+            st[k] = srci >= 0 ? a.proj[(size_t)(start + srci) * a.ldp + a.x_off + c] : st[k + len];
+        }
+    }
+    float A[SCAN_MAXS], S[SCAN_MAXS];
+    float* sst = a.ssm_state + ((size_t)slot * a.inner + c) * a.N;
+#pragma unroll
+    for (int e = 0; e < SCAN_MAXS; e++) {
+        const int n = lane + 32 * e;
+        A[e] = n < a.N ? -expf(a.A_log[(size_t)c * a.N + n]) : 0.f;
+        S[e] = n < a.N ? sst[n] : 0.f;
+    }
+    const float Dc = a.D[c], dtb = a.dt_bias[c];
+    for (int i = 0; i < len; i++) {
+        const int t = start + i;
+        const float dt = softplus_f(a.dt_raw[(size_t)t * a.inner + c] + dtb);
+        const float xv = a.xc[(size_t)t * a.inner + c];
+        const float* Bp = a.xproj + (size_t)t * a.ldx + a.R;
+        const float* Cp = Bp + a.N;
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < SCAN_MAXS; e++) {
+            const int n = lane + 32 * e;
+            if (n < a.N) {
+                S[e] = expf(dt * A[e]) * S[e] + dt * xv * Bp[n];
+                part = fmaf(S[e], Cp[n], part);
+            }
+        }
+        const float yv = warp_sum(part) + Dc * xv;
+        if (lane == 0) a.y[(size_t)t * a.inner + c] = yv * silu_f(a.proj[(size_t)t * a.ldp + a.z_off + c]);
+    }
+#pragma unroll
+    for (int e = 0; e < SCAN_MAXS; e++) { const int n = lane + 32 * e; if (n < a.N) sst[n] = S[e]; }
+}
+cudaError_t scan_recurrence_launch(const ScanArgs& a, const RaggedDev& r, cudaStream_t s) {
+    if (a.N > SCAN_MAXS * 32) return cudaErrorInvalidValue;
+    return launch_chain(scan_recurrence_kernel, dim3(r.n_seg, (a.inner + 7) / 8), dim3(256), 0, s, a, r);
+}
+
+// ---------------------------------------------------------------- matrix memory (mLSTM)
+// grid (n_seg, H, ceil(dv / 32)): a CTA owns 32 columns of one head's d x dv memory. Thread (col, grp) keeps rows grp, grp + RG,
+// ... of its column in registers (at most MM_ROWS). Per token: stage q, k, v in shared memory, decay + rank-one update,
+// partial read-out per row group, fixed-order sum of the groups. The normaliser n and the running maximum m are carried
+// by every CTA of the head (same arithmetic, same values); the first one writes them back. Two block barriers per token.
+constexpr int MM_ROWS = 16, MM_COLS = 32;      // key size <= 16 * 16 = 256 (512 threads)
+__global__ void __launch_bounds__(512) matrix_mem_kernel(MatrixMemArgs a, RaggedDev r, int RG) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float sm[];
+    const int d = a.d, dv = a.dv;
+    float* qs = sm;                    // [2][d]
+    float* ks = qs + 2 * d;            // [2][d]
+    float* vs = ks + 2 * d;            // [2][MM_COLS]
+    float* red = vs + 2 * MM_COLS;     // [RG][MM_COLS + 1]: partial read-outs, last column = partial n.q
+    const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * MM_COLS;
+    const int slot = r.seg_slot[seg], start = r.seg_start[seg], len = r.seg_len[seg];
+    const int lc = threadIdx.x % MM_COLS, grp = threadIdx.x / MM_COLS, col = c0 + lc;
+    const bool col_ok = col < dv;
+    float* Sg = a.S + (((size_t)slot * a.H + h) * d) * dv;
+    float* ng = a.n + ((size_t)slot * a.H + h) * d;
+    float S[MM_ROWS], nr[MM_ROWS];
+#pragma unroll
+    for (int i = 0; i < MM_ROWS; i++) {
+        const int row = grp + i * RG;
+        S[i] = (col_ok && row < d) ? Sg[(size_t)row * dv + col] : 0.f;
+        nr[i] = row < d ? ng[row] : 0.f;        // every column's thread carries the same copy of its rows of n
+    }
+    float m = a.m[(size_t)slot * a.H + h];
+    const float qscale = 1.f / sqrtf((float)d);
+    for (int i = 0; i < len; i++) {
+        const int t = start + i, buf = i & 1;
+        const float* p = a.proj + (size_t)t * a.ldp;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            qs[buf * d + j] = p[a.q_off + h * d + j] * qscale;
+            ks[buf * d + j] = p[a.k_off + h * d + j];
+        }
+        if (threadIdx.x < MM_COLS) vs[buf * MM_COLS + threadIdx.x] = col_ok ? p[a.v_off + h * dv + col] : 0.f;
+        // gates: capped pre-activations, log-space; every thread computes the same scalars
+        const float ig = a.cap * tanhf((p[a.i_off + h] + a.i_bias[h]) / a.cap);
+        const float fg = log_sigmoid_f(a.cap * tanhf((p[a.f_off + h] + a.f_bias[h]) / a.cap));
+        const float m_new = fmaxf(fg + m, ig);
+        const float da = expf(fg + m - m_new), ib = expf(ig - m_new);
+        m = m_new;
+        __syncthreads();
+        {
+            const float vb = ib * vs[buf * MM_COLS + lc];
+            float part = 0.f, npart = 0.f;
+#pragma unroll
+            for (int k = 0; k < MM_ROWS; k++) {
+                const int row = grp + k * RG;
+                if (row < d) {
+                    const float kk = ks[buf * d + row], qq = qs[buf * d + row];
+                    S[k] = fmaf(da, S[k], kk * vb);
+                    nr[k] = fmaf(da, nr[k], ib * kk);
+                    part = fmaf(S[k], qq, part);
+                    npart = fmaf(nr[k], qq, npart);
+                }
+            }
+            red[grp * (MM_COLS + 1) + lc] = part;
+            if (lc == 0) red[grp * (MM_COLS + 1) + MM_COLS] = npart;
+        }
+        __syncthreads();
+        if (threadIdx.x < MM_COLS && col_ok) {
+            float num = 0.f, nq = 0.f;
+            for (int g2 = 0; g2 < RG; g2++) { num += red[g2 * (MM_COLS + 1) + lc]; nq += red[g2 * (MM_COLS + 1) + MM_COLS]; }
+            const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+            a.o_raw[(size_t)t * a.H * dv + (size_t)h * dv + col] = num / den;
+        }
+        // the next token stages into the other q/k/v buffer and writes `red` only after its own first barrier
+    }
+#pragma unroll
+    for (int i = 0; i < MM_ROWS; i++) {
+        const int row = grp + i * RG;
+        if (row < d) {
+            if (col_ok) Sg[(size_t)row * dv + col] = S[i];
+            if (lc == 0 && blockIdx.z == 0) ng[row] = nr[i];
+        }
+    }
+    if (threadIdx.x == 0 && blockIdx.z == 0) a.m[(size_t)slot * a.H + h] = m;
+}
+
+// per (token, head): out = o / rms(o) * norm_w * sigmoid(gate)
+__global__ void __launch_bounds__(128) matrix_mem_out_kernel(MatrixMemArgs a) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t base = (size_t)t * a.H * a.dv + (size_t)h * a.dv;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.dv; i += blockDim.x) { const float v = a.o_raw[base + i]; ss += v * v; }
+    const float rinv = 1.f / sqrtf(block_sum(ss, red) / (float)a.dv + a.eps);
+    for (int i = threadIdx.x; i < a.dv; i += blockDim.x) {
+        const float gate = sigmoid_f(a.proj[(size_t)t * a.ldp + a.g_off + h * a.dv + i]);
+        a.out[base + i] = a.o_raw[base + i] * rinv * a.norm_w[h * a.dv + i] * gate;
+    }
+}
+
+cudaError_t matrix_mem_launch(const MatrixMemArgs& a, const RaggedDev& r, cudaStream_t s) {
+    if (a.dv <= 0 || a.d <= 0 || a.d > MM_ROWS * 16) return cudaErrorInvalidValue;
+    const int RG = (a.d + MM_ROWS - 1) / MM_ROWS;
+    const size_t smem = (size_t)(4 * a.d + 2 * MM_COLS + RG * (MM_COLS + 1)) * 4;
+    cudaError_t ce = launch_chain(matrix_mem_kernel, dim3(r.n_seg, a.H, (a.dv + MM_COLS - 1) / MM_COLS), dim3(RG * MM_COLS), smem, s, a, r, RG);
+    if (ce != cudaSuccess) return ce;
+    return launch_chain(matrix_mem_out_kernel, dim3(r.T, a.H), dim3(128), 0, s, a);
+}
+
+}  // namespace b2

@@ -32,15 +32,17 @@
 namespace b2 {
 
 enum GgmlType { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11,
-                T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14 };
+                T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_I32 = 26, T_BF16 = 30 };
 
 B2_HD int block_elems(int t) {
-    return (t == T_F32 || t == T_F16) ? 1 : (t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1) ? 32 : 256;
+    return (t == T_F32 || t == T_F16 || t == T_BF16 || t == T_I32) ? 1 : (t == T_Q4_0 || t == T_Q8_0 || t == T_Q4_1 || t == T_Q5_0 || t == T_Q5_1) ? 32 : 256;
 }
 B2_HD int block_bytes(int t) {
     switch (t) {
         case T_F32: return 4;
         case T_F16: return 2;
+        case T_BF16: return 2;
+        case T_I32: return 4;
         case T_Q4_0: return 18;
         case T_Q4_1: return 20;
         case T_Q5_0: return 22;

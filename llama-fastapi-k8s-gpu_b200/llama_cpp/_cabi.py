@@ -13,13 +13,30 @@ from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libb200gguf.so")
 
-B2_FLAG_NO_GRAPH, B2_FLAG_NO_PDL, B2_FLAG_ACT8 = 1, 2, 4
+B2_FLAG_NO_GRAPH, B2_FLAG_NO_PDL, B2_FLAG_ACT8, B2_FLAG_F32 = 1, 2, 4, 8
+B2_TYPE_F32, B2_TYPE_F16, B2_TYPE_I32, B2_TYPE_BF16 = 0, 1, 26, 30
+B2_MIX_WINDOW_SCAN, B2_MIX_MATRIX_MEMORY = 1, 2
+B2_STEP_MAX_ENTRIES = 64
 
 
 class B2Config(ctypes.Structure):
     _fields_ = [(n, c_int32) for n in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab")] + [
         ("rms_eps", c_float), ("rope_freq_base", c_float)] + [
         (n, c_int32) for n in ("n_ctx", "max_seqs", "kv_block_tokens", "kv_num_blocks", "device", "flags")]
+
+
+class B2LayerDesc(ctypes.Structure):
+    """b2_layer_desc: one layer of a layer-list model (mixer kind, its sizes and constants, feed-forward width)."""
+    _fields_ = [(n, c_int32) for n in ("mixer", "n_ff", "n_head", "n_head_kv", "head_dim", "rot_dims", "window", "keep_first",
+                                       "rope_orig_ctx", "pad0_")] + [
+        (n, c_double) for n in ("attn_scale", "rope_base", "rope_factor", "rope_fast", "rope_slow")] + [
+        (n, c_int32) for n in ("conv_taps", "dt_rank", "d_inner", "d_state", "mm_heads", "mm_dim", "mm_vdim", "pad_")] + [
+        ("gate_cap", c_double)]
+
+
+class B2LayeredConfig(ctypes.Structure):
+    _fields_ = [(n, c_int32) for n in ("n_layer", "n_embd", "n_vocab")] + [("norm_eps", c_float), ("residual_scale", c_float)] + [
+        (n, c_int32) for n in ("n_ctx", "max_seqs", "kv_block_tokens", "kv_num_blocks", "max_step_tokens", "device", "flags")]
 
 
 class B2Sampling(ctypes.Structure):
@@ -51,6 +68,13 @@ SIGNATURES = {
     "b2_forward_pending": (c_int, [c_void_p, c_int]),
     "b2_get_logits": (c_int, [c_void_p, c_int, c_void_p]),
     "b2_synchronize": (c_int, [c_void_p]),
+    "b2_engine_create_layered": (c_int, [POINTER(B2LayeredConfig), POINTER(B2LayerDesc), POINTER(c_void_p)]),
+    "b2_step": (c_int, [c_void_p, c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), c_int, c_void_p,
+                        POINTER(c_int32), POINTER(c_int32)]),
+    "b2_step_trace": (c_int, [c_void_p, c_int]),
+    "b2_step_trace_read": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "b2_step_profile": (c_int, [c_void_p, c_int]),
+    "b2_step_profile_read": (c_int, [c_void_p, POINTER(c_float), POINTER(c_int32)]),
     "b2_timer_start": (c_int, [c_void_p]),
     "b2_timer_stop": (c_int, [c_void_p, POINTER(c_float)]),
     "b2_kernel_launch_count": (c_int, [c_void_p, POINTER(c_int64)]),

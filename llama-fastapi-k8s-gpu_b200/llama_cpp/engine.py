@@ -73,7 +73,76 @@ def read_dims(g: GGUFFile) -> ModelDims:
         n_ctx_train=int(k("context_length", 2048)))
 
 
-class Engine:
+class EngineBase:
+    """What every native engine handle shares: lifecycle, sequence slots with their page tables, the device sampler,
+    logits read-back and the measurement hooks. `Engine` adds the llama graph's calls, `LayeredEngine` the ragged step."""
+    ragged = False      # True: the scheduler drives `step()` (prompt portions and decoded tokens in one batch)
+
+    # ---------------------------------------------------------------- lifecycle
+    def close(self):
+        if getattr(self, "_h", None):
+            self.lib.b2_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---------------------------------------------------------------- sequences
+    def seq_begin(self, slot: int, n_past: int, history: Sequence[int], sampling: SamplingSettings,
+                  uniforms: Optional[np.ndarray] = None):
+        hist = list(history)[-64:]
+        ha = (ctypes.c_int32 * max(1, len(hist)))(*hist)
+        sp = sampling.to_c()
+        if uniforms is None:
+            uniforms = np.zeros(1, dtype=np.float64)
+        u = np.ascontiguousarray(uniforms[:8192], dtype=np.float64)
+        check(self.lib.b2_seq_begin(self._h, slot, n_past, ha, len(hist), ctypes.byref(sp),
+                                    u.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), len(u)), "b2_seq_begin")
+
+    def ensure_pages(self, slot: int, n_tokens: int):
+        """Make sure the slot's page table covers n_tokens positions (uploads it if it grew)."""
+        if self.pages.ensure(slot, n_tokens):
+            tbl = self.pages.table(slot)
+            arr = (ctypes.c_int32 * len(tbl))(*tbl)
+            check(self.lib.b2_seq_set_blocks(self._h, slot, arr, len(tbl)), "b2_seq_set_blocks")
+
+    def release(self, slot: int):
+        self.pages.release(slot)
+
+    def sample(self, slot: int) -> int:
+        out = ctypes.c_int32()
+        check(self.lib.b2_sample(self._h, slot, ctypes.byref(out)), "b2_sample")
+        return out.value
+
+    def logits(self, slot: int) -> np.ndarray:
+        out = np.empty(self.dims.n_vocab, dtype=np.float32)
+        check(self.lib.b2_get_logits(self._h, slot, out.ctypes.data_as(ctypes.c_void_p)), "b2_get_logits")
+        return out
+
+    # ---------------------------------------------------------------- measurement
+    def timer_start(self):
+        check(self.lib.b2_timer_start(self._h), "b2_timer_start")
+
+    def timer_stop(self) -> float:
+        ms = ctypes.c_float()
+        check(self.lib.b2_timer_stop(self._h, ctypes.byref(ms)), "b2_timer_stop")
+        return ms.value
+
+    def launch_count(self) -> int:
+        n = ctypes.c_int64()
+        check(self.lib.b2_kernel_launch_count(self._h, ctypes.byref(n)))
+        return n.value
+
+    def device_bytes(self):
+        w, kv = ctypes.c_int64(), ctypes.c_int64()
+        check(self.lib.b2_engine_device_bytes(self._h, ctypes.byref(w), ctypes.byref(kv)))
+        return w.value, kv.value
+
+
+class Engine(EngineBase):
     """One model on one GPU. Calls are serialised by `self.lock` (the native side also locks)."""
 
     def __init__(self, gguf: GGUFFile, n_ctx: int, max_seqs: int = 1, device: int = 0,
@@ -139,49 +208,10 @@ class Engine:
         check(_cabi.load_library().b2_tp_unique_id(buf), "b2_tp_unique_id")
         return bytes(buf)
 
-    # ---------------------------------------------------------------- lifecycle
-    def close(self):
-        if getattr(self, "_h", None):
-            self.lib.b2_engine_destroy(self._h)
-            self._h = None
-
-    def __del__(self):
-        try:
-            self.close()
-        except Exception:
-            pass
-
-    # ---------------------------------------------------------------- sequences
-    def seq_begin(self, slot: int, n_past: int, history: Sequence[int], sampling: SamplingSettings,
-                  uniforms: Optional[np.ndarray] = None):
-        hist = list(history)[-64:]
-        ha = (ctypes.c_int32 * max(1, len(hist)))(*hist)
-        sp = sampling.to_c()
-        if uniforms is None:
-            uniforms = np.zeros(1, dtype=np.float64)
-        u = np.ascontiguousarray(uniforms[:8192], dtype=np.float64)
-        check(self.lib.b2_seq_begin(self._h, slot, n_past, ha, len(hist), ctypes.byref(sp),
-                                    u.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), len(u)), "b2_seq_begin")
-
-    def ensure_pages(self, slot: int, n_tokens: int):
-        """Make sure the slot's page table covers n_tokens positions (uploads it if it grew)."""
-        if self.pages.ensure(slot, n_tokens):
-            tbl = self.pages.table(slot)
-            arr = (ctypes.c_int32 * len(tbl))(*tbl)
-            check(self.lib.b2_seq_set_blocks(self._h, slot, arr, len(tbl)), "b2_seq_set_blocks")
-
-    def release(self, slot: int):
-        self.pages.release(slot)
-
     # ---------------------------------------------------------------- forward
     def prefill(self, slot: int, tokens: Sequence[int]):
         arr = (ctypes.c_int32 * len(tokens))(*tokens)
         check(self.lib.b2_prefill(self._h, slot, arr, len(tokens)), "b2_prefill")
-
-    def sample(self, slot: int) -> int:
-        out = ctypes.c_int32()
-        check(self.lib.b2_sample(self._h, slot, ctypes.byref(out)), "b2_sample")
-        return out.value
 
     def decode(self, slots: Sequence[int]) -> List[int]:
         n = len(slots)
@@ -207,25 +237,6 @@ class Engine:
     def forward_pending(self, slot: int):
         check(self.lib.b2_forward_pending(self._h, slot), "b2_forward_pending")
 
-    def logits(self, slot: int) -> np.ndarray:
-        out = np.empty(self.dims.n_vocab, dtype=np.float32)
-        check(self.lib.b2_get_logits(self._h, slot, out.ctypes.data_as(ctypes.c_void_p)), "b2_get_logits")
-        return out
-
-    # ---------------------------------------------------------------- measurement
-    def timer_start(self):
-        check(self.lib.b2_timer_start(self._h), "b2_timer_start")
-
-    def timer_stop(self) -> float:
-        ms = ctypes.c_float()
-        check(self.lib.b2_timer_stop(self._h, ctypes.byref(ms)), "b2_timer_stop")
-        return ms.value
-
-    def launch_count(self) -> int:
-        n = ctypes.c_int64()
-        check(self.lib.b2_kernel_launch_count(self._h, ctypes.byref(n)))
-        return n.value
-
     def mode(self) -> dict:
         v = [ctypes.c_int() for _ in range(5)]
         check(self.lib.b2_engine_mode(self._h, *[ctypes.byref(x) for x in v]))
@@ -237,11 +248,6 @@ class Engine:
             out.update(tp_rank=t[0].value, tp_world=t[1].value, tp_allreduce="peer memory" if t[2].value else "nccl")
         return out
 
-    def device_bytes(self):
-        w, kv = ctypes.c_int64(), ctypes.c_int64()
-        check(self.lib.b2_engine_device_bytes(self._h, ctypes.byref(w), ctypes.byref(kv)))
-        return w.value, kv.value
-
     def profile_decode_step(self, slot: int):
         ms = (ctypes.c_float * 8)()
         nl = (ctypes.c_int32 * 8)()
@@ -249,3 +255,132 @@ class Engine:
         check(self.lib.b2_profile_decode_step(self._h, slot, ms, nl, by), "b2_profile_decode_step")
         kinds = ["embed", "qkv", "attention", "attn_out", "gate_up", "ffn_down", "lm_head", "sampler"]
         return {k: dict(ms=ms[i], launches=nl[i], bytes=by[i]) for i, k in enumerate(kinds)}
+
+
+class LayeredEngine(EngineBase):
+    """A layer-list model (dense bf16 / f32 tensors, `b2_engine_create_layered`) on one GPU, stepped over ragged batches.
+
+    `kv_tokens` sizes the page pool (shared by all sequences); `n_ctx` bounds one sequence. `dtype` "float32" runs every
+    product in true 32-bit with f32 cache pages; "bfloat16" is the serving path (tensor-core products, bf16 pages; norms,
+    softmax, gates and recurrent state stay 32-bit)."""
+    ragged = True
+
+    def __init__(self, dims, tensors, n_ctx: int, max_seqs: int = 4, device: int = 0, kv_block_tokens: int = 64,
+                 flags: int = 0, dtype: str = "bfloat16", kv_tokens: Optional[int] = None,
+                 max_step_tokens: Optional[int] = None, verbose: bool = False, tp=None):
+        if tp:
+            raise ValueError("layer-list models are not tensor-parallel")
+        if dtype not in ("bfloat16", "float32"):
+            raise ValueError(f"dtype must be bfloat16 or float32, not {dtype!r}")
+        self.lib = _cabi.load_library()
+        self.dims = dims
+        self.dtype = dtype
+        self.n_ctx, self.max_seqs, self.device = int(n_ctx), int(max_seqs), int(device)
+        self.block_tokens = int(kv_block_tokens)
+        self.tp_rank, self.tp_world = 0, 1
+        per_seq = (self.n_ctx + self.block_tokens - 1) // self.block_tokens
+        n_pages = per_seq * self.max_seqs if kv_tokens is None else (int(kv_tokens) + self.block_tokens - 1) // self.block_tokens
+        self.pages = PageAllocator(max(1, n_pages), self.block_tokens)
+        self.max_step_tokens = int(max_step_tokens or min(max(self.n_ctx, 64), 2048))
+        if os.environ.get("B2_NO_PDL"):
+            flags |= _cabi.B2_FLAG_NO_PDL
+        if dtype == "float32":
+            flags |= _cabi.B2_FLAG_F32
+        cfg = _cabi.B2LayeredConfig(dims.n_layer, dims.n_embd, dims.n_vocab, dims.norm_eps, dims.residual_scale, self.n_ctx,
+                                    self.max_seqs, self.block_tokens, self.pages.num_blocks, self.max_step_tokens, self.device, flags)
+        descs = (_cabi.B2LayerDesc * dims.n_layer)(*dims.layers)
+        h = ctypes.c_void_p()
+        check(self.lib.b2_engine_create_layered(ctypes.byref(cfg), descs, ctypes.byref(h)), "b2_engine_create_layered")
+        self._h = h
+        self.lock = threading.RLock()
+        type_ids = {"BF16": _cabi.B2_TYPE_BF16, "F32": _cabi.B2_TYPE_F32}
+        try:
+            for name, t in tensors.items():
+                if t.dtype not in type_ids:
+                    raise ValueError(f"tensor {name}: dtype {t.dtype} is not supported (BF16 or F32)")
+                shape = tuple(t.shape)
+                ne0 = shape[-1] if shape else 1
+                ne1 = int(np.prod(shape[:-1])) if len(shape) > 1 else 1
+                data = np.ascontiguousarray(t.data)
+                check(self.lib.b2_upload_tensor(self._h, name.encode(), type_ids[t.dtype], ne0, ne1,
+                                                data.ctypes.data_as(ctypes.c_void_p), data.nbytes), f"upload {name}")
+            check(self.lib.b2_engine_finalize(self._h), "b2_engine_finalize")
+        except Exception:
+            self.close()
+            raise
+
+    # ---------------------------------------------------------------- forward
+    def step(self, entries, want=None, sample=None):
+        """One ragged step. entries: [(slot, [token, ...]), ...]; want: per entry, indices into its tokens whose logits are
+        asked for; sample: per entry, whether to sample after its last token. Returns (logits [n_wanted, n_vocab] in entry
+        order, [sampled token or None per entry]). A batch larger than `max_step_tokens` is run as several native steps,
+        cutting entries where needed (the result does not depend on the cut)."""
+        n = len(entries)
+        want = want if want is not None else [[] for _ in entries]
+        sample = sample if sample is not None else [False] * n
+        n_want = sum(len(w) for w in want)
+        logits = np.empty((n_want, self.dims.n_vocab), dtype=np.float32)
+        sampled = [None] * n
+        base, acc = [], 0
+        for w in want:
+            base.append(acc)
+            acc += len(w)
+        cursor = [0] * n          # tokens of each entry already run
+        while True:
+            room, batch = self.max_step_tokens, []
+            for i, (slot, toks) in enumerate(entries):
+                left = len(toks) - cursor[i]
+                if left <= 0 or room <= 0 or len(batch) >= _cabi.B2_STEP_MAX_ENTRIES:
+                    continue
+                take = min(left, room)
+                batch.append((i, cursor[i], take))
+                room -= take
+            if not batch:
+                break
+            slots = (ctypes.c_int32 * len(batch))(*[entries[i][0] for i, _, _ in batch])
+            counts = (ctypes.c_int32 * len(batch))(*[k for _, _, k in batch])
+            flat, rows, dest, flags = [], [], [], []
+            for i, lo, k in batch:
+                toks = entries[i][1]
+                for j, wi in enumerate(want[i]):
+                    if lo <= wi < lo + k:
+                        rows.append(len(flat) + wi - lo)
+                        dest.append(base[i] + j)
+                flat.extend(toks[lo:lo + k])
+                flags.append(1 if (sample[i] and lo + k == len(toks)) else 0)
+            tok_arr = (ctypes.c_int32 * len(flat))(*flat)
+            row_arr = (ctypes.c_int32 * max(1, len(rows)))(*rows)
+            flag_arr = (ctypes.c_int32 * len(batch))(*flags)
+            out_tok = (ctypes.c_int32 * len(batch))()
+            part = np.empty((max(1, len(rows)), self.dims.n_vocab), dtype=np.float32)
+            check(self.lib.b2_step(self._h, len(batch), slots, counts, tok_arr, row_arr, len(rows),
+                                   part.ctypes.data_as(ctypes.c_void_p), flag_arr, out_tok), "b2_step")
+            for r, dst in enumerate(dest):
+                logits[dst] = part[r]
+            for b, (i, lo, k) in enumerate(batch):
+                cursor[i] = lo + k
+                if flags[b]:
+                    sampled[i] = int(out_tok[b])
+        return logits, sampled
+
+    def trace_layers(self, on: bool = True):
+        check(self.lib.b2_step_trace(self._h, 1 if on else 0), "b2_step_trace")
+
+    def layer_outputs(self, n_tokens: int) -> np.ndarray:
+        """Residual stream after every layer for the tokens of the last native step: [n_layer, n_tokens, n_embd]."""
+        out = np.empty((self.dims.n_layer, n_tokens, self.dims.n_embd), dtype=np.float32)
+        check(self.lib.b2_step_trace_read(self._h, out.ctypes.data_as(ctypes.c_void_p), self.dims.n_layer, n_tokens), "b2_step_trace_read")
+        return out
+
+    def profile(self, on: bool = True):
+        check(self.lib.b2_step_profile(self._h, 1 if on else 0), "b2_step_profile")
+
+    def profile_read(self) -> dict:
+        ms = (ctypes.c_float * 8)()
+        nl = (ctypes.c_int32 * 8)()
+        check(self.lib.b2_step_profile_read(self._h, ms, nl), "b2_step_profile_read")
+        kinds = ["embed", "dense", "attention", "scan", "matrix_memory", "norms", "head"]
+        return {k: dict(ms=ms[i], launches=nl[i]) for i, k in enumerate(kinds)}
+
+    def mode(self) -> dict:
+        return dict(graph=False, pdl=not os.environ.get("B2_NO_PDL"), dtype=self.dtype, max_step_tokens=self.max_step_tokens)

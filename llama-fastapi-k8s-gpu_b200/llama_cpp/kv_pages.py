@@ -64,3 +64,56 @@ class PageAllocator:
             keep = self.pages_for(n_tokens)
             while len(pages) > keep:
                 self._free.append(pages.pop())
+
+
+class SequenceSlots:
+    """Sequence slots of one engine: a slot is a page table plus, for models with recurrent layers, one state slot on
+    the device. `open` binds a caller's key to a free slot and starts the sequence from nothing (the engine zeroes the
+    slot's recurrent state; pages are taken as the sequence grows), `close` gives the pages and the slot back for the
+    next sequence. Used by the trace runner and by anything else that steps an engine without the request scheduler."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self._free: List[int] = list(range(engine.max_seqs - 1, -1, -1))
+        self._slot: Dict[object, int] = {}
+        self._len: Dict[object, int] = {}
+
+    def __contains__(self, key) -> bool:
+        return key in self._slot
+
+    def slot(self, key) -> int:
+        return self._slot[key]
+
+    def length(self, key) -> int:
+        return self._len[key]
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free)
+
+    def open(self, key, sampling=None, uniforms=None) -> int:
+        if key in self._slot:
+            raise ValueError(f"sequence {key!r} is already open")
+        if not self._free:
+            raise RuntimeError(f"all {self.engine.max_seqs} sequence slots are in use")
+        slot = self._free.pop()
+        if sampling is None:
+            from .engine import SamplingSettings
+            sampling = SamplingSettings(temperature=0.0, repeat_penalty=1.0)
+        self.engine.release(slot)
+        self.engine.seq_begin(slot, 0, [], sampling, uniforms)
+        self._slot[key], self._len[key] = slot, 0
+        return slot
+
+    def extend(self, key, n_tokens: int) -> int:
+        """Reserve pages for n_tokens more tokens of the sequence; returns its slot."""
+        slot = self._slot[key]
+        self._len[key] += int(n_tokens)
+        self.engine.ensure_pages(slot, self._len[key])
+        return slot
+
+    def close(self, key) -> None:
+        slot = self._slot.pop(key)
+        self._len.pop(key)
+        self.engine.release(slot)
+        self._free.append(slot)
