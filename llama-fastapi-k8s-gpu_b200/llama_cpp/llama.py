@@ -21,7 +21,7 @@ import numpy as np
 
 from . import chat_format as cf
 from .engine import Engine, SamplingSettings
-from .gguf_file import GGUFFile
+from . import models
 from .sampling import UniformStream
 from .scheduler import Request, Scheduler
 from .tokenizer import Vocab
@@ -47,25 +47,34 @@ class Llama:
                              "(pass n_gpu_layers=-1 as /root/reference/api.py:26 does)")
         self.model_path = model_path
         self.verbose = verbose
-        self._gguf = GGUFFile(model_path)
-        self.metadata: Dict[str, Any] = {k: v for k, v in self._gguf.metadata.items()
+        self._source = models.open_model(model_path)      # a GGUF file, or a folder with config.json + model.safetensors
+        self._gguf = self._source.gguf
+        self._md = self._source.metadata or {}
+        self.metadata: Dict[str, Any] = {k: v for k, v in self._md.items()
                                          if isinstance(v, (str, int, float, bool))}
-        dims_ctx = int(self._gguf.metadata.get("llama.context_length", 2048))
+        dims_ctx = int(self._md.get("llama.context_length", 2048))
         self._n_ctx = int(n_ctx) if n_ctx else dims_ctx
         self._seed = seed
         self.last_n_tokens_size = min(int(last_n_tokens_size), 64)
         max_seqs = int(n_seq_max or os.environ.get("B200_MAX_SEQS", "1"))
         device = int(os.environ.get("B200_DEVICE", main_gpu))
-        self._engine = Engine(self._gguf, n_ctx=self._n_ctx, max_seqs=max_seqs, device=device,
-                              kv_block_tokens=int(os.environ.get("B200_KV_BLOCK", "64")), tp=tp)
-        self._vocab = Vocab(self._gguf.metadata, self._engine.dims.n_vocab)
+        kv_block = int(os.environ.get("B200_KV_BLOCK", "64"))
+        if self._source.family.source == "gguf":
+            self._engine = Engine(self._gguf, n_ctx=self._n_ctx, max_seqs=max_seqs, device=device, kv_block_tokens=kv_block, tp=tp)
+        else:       # folder models: the family's own engine; compute dtype "bfloat16" (serving path) or "float32"
+            dtype = kwargs.get("dtype") or os.environ.get("B200_DTYPE", "bfloat16")
+            self._engine = models.open_engine(self._source, n_ctx=self._n_ctx, max_seqs=max_seqs, device=device,
+                                              kv_block_tokens=kv_block, tp=tp, dtype=dtype)
+        self._ragged = bool(getattr(self._engine, "ragged", False))
+        self._vocab = Vocab(self._md, self._engine.dims.n_vocab)
+        self._last_logits = None
         self._scheduler = Scheduler(self._engine, self._vocab)
         self._stream = UniformStream(seed)
         self._stream_lock = threading.Lock()
         # chat format selection (upstream Llama.__init__)
         self.chat_format = chat_format
         self._chat_formatter = None
-        md = self._gguf.metadata
+        md = self._md
         if self.chat_format is None and "tokenizer.chat_template" in md:
             guess = cf.guess_chat_format_from_gguf_metadata(md)
             if guess is not None:
@@ -136,7 +145,17 @@ class Llama:
             if len(self._input_ids) + len(toks) > self._n_ctx:
                 raise ValueError(f"Requested tokens ({len(self._input_ids) + len(toks)}) exceed context window of {self._n_ctx}")
             self._scheduler.drop_cache()
+            if self._ragged and not self._direct_open:
+                eng.release(0)
             eng.ensure_pages(0, len(self._input_ids) + len(toks))
+            if self._ragged:
+                if not self._direct_open:
+                    eng.seq_begin(0, 0, [], SamplingSettings(temperature=0.0, repeat_penalty=1.0))
+                    self._direct_open = True
+                logits, _ = eng.step([(0, toks)], want=[[len(toks) - 1]])
+                self._last_logits = logits[0]
+                self._input_ids.extend(toks)
+                return
             if not self._direct_open:
                 eng.seq_begin(0, 0, [], SamplingSettings(temperature=0.0, repeat_penalty=1.0))
                 self._direct_open = True
@@ -151,6 +170,10 @@ class Llama:
     def scores(self) -> np.ndarray:
         """Logits of the last evaluated token, shape [1, n_vocab] (upstream keeps all rows)."""
         with self._engine.lock:
+            if self._ragged:
+                if self._last_logits is None:
+                    raise RuntimeError("scores: nothing has been evaluated yet")
+                return self._last_logits[None, :]
             return self._engine.logits(0)[None, :]
 
     # ------------------------------------------------------------------ completion

@@ -64,6 +64,7 @@ class _Slot:
         self.req: Optional[Request] = None
         self.cached: List[int] = []       # tokens whose K/V are in this slot's pages
         self.pending: int = -1            # sampled, not yet forwarded
+        self.fed: int = 0                 # ragged engines: prompt tokens already run
 
 
 def check_token(req: Request, vocab: Vocab, tok: int) -> bool:
@@ -99,6 +100,7 @@ def check_token(req: Request, vocab: Vocab, tok: int) -> bool:
 class Scheduler:
     RUN_AHEAD = 8
     ADMIT_PER_STEP = 2     # while sequences are decoding, at most this many new prompts are processed between two decode steps
+    PROMPT_PORTION = 512   # ragged engines: most prompt tokens one sequence brings into a step (decoding sequences ride along)
 
     def __init__(self, engine: Engine, vocab: Vocab):
         self.engine = engine
@@ -177,11 +179,12 @@ class Scheduler:
                     if s.req is not None and s.req.cancelled():
                         self._cancelled(s.req)
                         s.req = None
+                ragged = getattr(self.engine, "ragged", False)
                 for req in admitted:
-                    self._admit(req)
+                    (self._admit_ragged if ragged else self._admit)(req)
                 t1 = time.perf_counter()
                 d0 = self.stats["t_decode"]
-                self._step(waiting)
+                (self._step_ragged if ragged else self._step)(waiting)
                 self.stats["t_admit"] += t1 - t0
                 self.stats["t_host"] += (time.perf_counter() - t1) - (self.stats["t_decode"] - d0)
 
@@ -204,6 +207,9 @@ class Scheduler:
     def _finish(self, slot: _Slot):
         req = slot.req
         slot.req = None
+        if getattr(self.engine, "ragged", False):      # recurrent state cannot serve as a cached prefix: pages go back now
+            slot.cached = []
+            self.engine.release(slot.idx)
         req.t_done = time.perf_counter()
         self.stats["last_done"] = req.t_done
         req.done.set()
@@ -283,3 +289,61 @@ class Scheduler:
             for s in live:
                 if s.req is not None:
                     self._fail(s, exc)
+
+    # ------------------------------------------------------------------ ragged engines (layer-list models)
+    def _admit_ragged(self, req: Request):
+        """Bind the request to a free slot; its prompt is run by the following steps, portion by portion, in the same
+        batches as the tokens of the sequences that are already decoding."""
+        slot = next(s for s in self.slots if s.req is None)
+        slot.req, slot.cached, slot.fed, slot.pending = req, [], 0, -1
+        eng = self.engine
+        try:
+            eng.release(slot.idx)
+            eng.ensure_pages(slot.idx, min(eng.n_ctx, len(req.prompt) + req.max_tokens + 1))
+            eng.seq_begin(slot.idx, 0, req.prompt[-64:], req.sampling, req.uniforms)
+        except BaseException as exc:  # noqa: BLE001 - forwarded to the caller
+            eng.release(slot.idx)
+            self._fail(slot, exc)
+
+    def _step_ragged(self, waiting: int):
+        live = [s for s in self.slots if s.req is not None]
+        if not live:
+            return
+        eng = self.engine
+        self.stats["max_batch"] = max(self.stats["max_batch"], len(live))
+        room = eng.max_step_tokens
+        batch = []           # (slot object, tokens, finishes its prompt / decodes)
+        for s in live:       # decoding sequences first: one token each
+            if s.fed >= len(s.req.prompt) and room > 0:
+                batch.append((s, [s.pending], True))
+                room -= 1
+        for s in live:
+            left = len(s.req.prompt) - s.fed
+            if left > 0 and room > 0:
+                take = min(left, self.PROMPT_PORTION, room)
+                batch.append((s, s.req.prompt[s.fed:s.fed + take], take == left))
+                room -= take
+        try:
+            td = time.perf_counter()
+            _, toks = eng.step([(s.idx, t) for s, t, _ in batch], sample=[last for _, _, last in batch])
+            self.stats["t_decode"] += time.perf_counter() - td
+            self.stats["steps"] += 1
+            for (s, t, last), tok in zip(batch, toks):
+                if s.fed < len(s.req.prompt):
+                    s.fed += len(t)
+                    self.stats["prefill_tokens"] += len(t)
+                    if not last:
+                        continue
+                    s.req.t_first = time.perf_counter()
+                else:
+                    self.stats["tokens"] += 1
+                s.cached.extend(t)
+                s.pending = tok
+                if check_token(s.req, self.vocab, tok):
+                    self._finish(s)
+        except BaseException as exc:  # noqa: BLE001
+            for s in live:
+                if s.req is not None:
+                    eng.release(s.idx)
+                    self._fail(s, exc)
+

@@ -258,16 +258,19 @@ def create_app(llms: List[Any], *, max_queue_size: int = MAX_QUEUE_SIZE, permits
     return app
 
 
-def load_replicas(model_path: str, gpus: List[int], n_ctx: int = MAX_CONTEXT_TOKENS, permits: int = 1) -> List[Any]:
-    """One `Llama` (engine + scheduler thread) per GPU; each batches up to `permits` concurrent callers."""
+def load_replicas(model_path: str, gpus: List[int], n_ctx: int = MAX_CONTEXT_TOKENS, permits: int = 1, dtype: str = "") -> List[Any]:
+    """One `Llama` (engine + scheduler thread) per GPU; each batches up to `permits` concurrent callers. `model_path` is a
+    GGUF file or a model folder (config.json + model.safetensors); `dtype` applies to the latter."""
     from . import Llama
-    return [Llama(model_path=model_path, n_gpu_layers=-1, n_ctx=n_ctx, main_gpu=g, n_seq_max=max(1, permits), verbose=False)
+    extra = {"dtype": dtype} if dtype else {}
+    return [Llama(model_path=model_path, n_gpu_layers=-1, n_ctx=n_ctx, main_gpu=g, n_seq_max=max(1, permits), verbose=False, **extra)
             for g in gpus]
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Serve the reference's /response API on B200 engines")
-    ap.add_argument("--model", required=True)
+    ap.add_argument("--model", required=True, help="GGUF file, or a folder with config.json + model.safetensors")
+    ap.add_argument("--dtype", default="", choices=["", "bfloat16", "float32"], help="compute dtype of folder models (default bfloat16)")
     ap.add_argument("--gpus", default="0", help="comma-separated CUDA device ordinals, one engine replica each")
     ap.add_argument("--n-ctx", type=int, default=MAX_CONTEXT_TOKENS)
     ap.add_argument("--queue", type=int, default=MAX_QUEUE_SIZE, help="queued requests per replica before 503 (api.py:19)")
@@ -280,7 +283,7 @@ def main(argv=None) -> int:
     import uvicorn
     logging.basicConfig(level=logging.INFO)
     gpus = [int(g) for g in args.gpus.split(",") if g != ""]
-    llms = load_replicas(args.model, gpus, args.n_ctx, args.permits)
+    llms = load_replicas(args.model, gpus, args.n_ctx, args.permits, args.dtype)
     app = create_app(llms, max_queue_size=args.queue, permits=args.permits, consumers=args.consumers, timeout_seconds=args.timeout,
                      max_context_tokens=args.n_ctx)
     uvicorn.run(app, host=args.host, port=args.port, log_level="info")
