@@ -474,13 +474,153 @@ def batch_workload(args, cfg, path, n_prompt, batch, rank, world, local_rank, ba
     return 0
 
 
+GOPONEX_SIZES = {      # name: (width, heads, kv heads, ff, llama arch of equal width / depth / ff)
+    "1k": (1024, 8, 2, 4096, "cmp-1k"),
+    "2k": (2048, 16, 4, 8192, "cmp-2k"),
+    "4k": (4096, 32, 8, 14336, "cmp-4k"),
+}
+
+
+def measured_peak_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops)"
+    except Exception:
+        return 1590.0, "fallback (1.59 PFLOP/s)"
+
+
+def goponex_workload(args):
+    """Prefill and decode throughput of the Goponex layer-list graph at three layer sizes (random bf16 weights, four layers:
+    mLSTM, 2 x attention+scan with feed-forward, mLSTM) beside the llama graph at equal width, depth and feed-forward size
+    (Q8_0 GGUF). Device time with CUDA events around the engine calls; per-kernel-kind times from one profiled step."""
+    import numpy as np
+    from llama_cpp import goponex, synth
+    from llama_cpp.engine import Engine, SamplingSettings
+    from llama_cpp.gguf_file import GGUFFile
+    from llama_cpp.kv_pages import SequenceSlots
+    hbm, hbm_src = measured_peak_gbs()
+    tfl, tfl_src = measured_peak_tflops()
+    n_prompt, n_dec, vocab = 2048, max(8, min(args.steps, 64)), 32000
+    rng = np.random.default_rng(0)
+    prompt = [int(t) for t in rng.integers(0, vocab, size=n_prompt)]
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    out, launches = {}, 0
+    for name in (args.sizes.split(",") if args.sizes else list(GOPONEX_SIZES)):
+        width, heads, kv, ff, llama_arch = GOPONEX_SIZES[name]
+        cfg, tensors = goponex.synthetic(width, heads, kv, ff, vocab)
+        eng = goponex.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
+        n_param = sum(int(np.prod(t.shape)) for k, t in tensors.items() if len(t.shape) == 2 and k != "embed")
+        del tensors
+        seqs = SequenceSlots(eng)
+        rec = {"params_per_token_matmul": n_param}
+
+        def prefill_once(key, profile=False):
+            seqs.open(key)
+            slot = seqs.extend(key, n_prompt)
+            eng.profile(profile)
+            eng.timer_start()
+            eng.step([(slot, prompt)], want=[[n_prompt - 1]])
+            ms = eng.timer_stop()
+            eng.profile(False)
+            return ms
+
+        for i in range(max(3, args.warmup // 4)):
+            prefill_once(f"w{i}")
+            seqs.close(f"w{i}")
+        l0 = eng.launch_count()
+        ms = min(prefill_once(f"p{i}") or 1e9 for i in range(1))
+        launches += eng.launch_count() - l0
+        rec["prefill_ms"], rec["prefill_tok_s"] = round(ms, 3), round(n_prompt / ms * 1e3, 1)
+        rec["prefill_tflops"] = round(2.0 * n_param * n_prompt / ms / 1e9, 1)
+        rec["prefill_frac_of_bf16_peak"] = round(rec["prefill_tflops"] / tfl, 3)
+        # decode: batch 1 (the sequence just prefilled), then 4 sequences per step
+        tok = [1]
+        slot = seqs.slot("p0")
+        for _ in range(3):
+            eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
+        eng.timer_start()
+        l0 = eng.launch_count()
+        for _ in range(n_dec):
+            eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
+        ms1 = eng.timer_stop() / n_dec
+        launches += eng.launch_count() - l0
+        w_bytes = 2.0 * n_param
+        rec["decode_bs1_ms"], rec["decode_bs1_tok_s"] = round(ms1, 4), round(1e3 / ms1, 1)
+        rec["decode_bs1_frac_of_hbm"] = round(w_bytes / (ms1 * 1e-3) / 1e9 / hbm, 3)
+        for k in ("q1", "q2", "q3"):
+            prefill_once(k)
+        keys = ["p0", "q1", "q2", "q3"]
+        for _ in range(3):
+            eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
+        eng.timer_start()
+        for _ in range(n_dec):
+            eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
+        ms4 = eng.timer_stop() / n_dec
+        rec["decode_bs4_ms"], rec["decode_bs4_tok_s"] = round(ms4, 4), round(4e3 / ms4, 1)
+        # per-kernel-kind device time of one profiled prompt pass and one profiled single-token step
+        for k in keys:
+            seqs.close(k)
+        prefill_once("prof", profile=True)
+        rec["prefill_kinds_ms"] = {k: round(v["ms"], 3) for k, v in eng.profile_read().items() if v["launches"]}
+        eng.profile(True)
+        eng.step([(seqs.extend("prof", 1), tok)], sample=[True])
+        rec["decode_kinds_ms"] = {k: round(v["ms"], 4) for k, v in eng.profile_read().items() if v["launches"]}
+        eng.profile(False)
+        eng.close()
+        # the llama graph at equal width / depth / feed-forward size
+        path = ensure_model(llama_arch, "Q8_0")
+        g = GGUFFile(path)
+        le = Engine(g, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=1)
+        l_param = sum(int(np.prod(t.shape)) for k, t in g.tensors.items() if len(t.shape) == 2 and k != "token_embd.weight")
+        greedy = SamplingSettings(temperature=0.0, repeat_penalty=1.0)
+        lp = [t % 32000 for t in prompt]
+        best = 1e9
+        for i in range(4):
+            le.ensure_pages(0, n_prompt + 4 * n_dec + 8)
+            le.seq_begin(0, 0, [], greedy)
+            le.timer_start()
+            le.prefill(0, lp)
+            t_ms = le.timer_stop()
+            if i:
+                best = min(best, t_ms)
+        le.sample(0)
+        le.decode_n(0, 4)
+        le.timer_start()
+        le.decode_n(0, n_dec)
+        lms1 = le.timer_stop() / n_dec
+        kinds = le.profile_decode_step(0)
+        le.close()
+        rec["llama"] = {"arch": llama_arch, "ftype": "Q8_0", "params_per_token_matmul": l_param,
+                        "prefill_ms": round(best, 3), "prefill_tok_s": round(n_prompt / best * 1e3, 1),
+                        "prefill_tflops": round(2.0 * l_param * n_prompt / best / 1e9, 1),
+                        "prefill_frac_of_bf16_peak": round(2.0 * l_param * n_prompt / best / 1e9 / tfl, 3),
+                        "decode_bs1_ms": round(lms1, 4), "decode_bs1_tok_s": round(1e3 / lms1, 1),
+                        "decode_bs1_frac_of_hbm": round(l_param * 34.0 / 32.0 / (lms1 * 1e-3) / 1e9 / hbm, 3),
+                        "decode_kinds_ms": {k: round(v["ms"], 4) for k, v in kinds.items() if v["launches"]}}
+        out[name] = rec
+    clocks = sampler.result()
+    line = {"metric": "goponex_prefill_tokens_per_s", "value": out[list(out)[-1]]["prefill_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": n_dec, "warmup": max(3, args.warmup // 4), "ms_per_step": out[list(out)[-1]]["decode_bs1_ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": "Goponex layer-list graph, 4 layers (mLSTM, 2 x attention+scan+MLP, mLSTM), random bf16 weights",
+                       "prompt_tokens": n_prompt, "decode_steps": n_dec, "global_batch": 1, "seq_len": n_prompt,
+                       "parallelism": "single GPU",
+                       "l2": "each step streams the whole weight set (0.2-2 GB, larger than the 126 MB L2); no flush needed"},
+            "sizes": out, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tfl, "bf16_source": tfl_src},
+            "clocks": clocks, "gpu_launches": int(launches)}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS) + ["goponex-sizes"])
+    ap.add_argument("--sizes", default="", help="goponex-sizes: comma-separated subset of 1k,2k,4k (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--batch-extra", type=int, default=32, help="bs1 workloads: also time this many sequences per step (0 = skip)")
@@ -490,6 +630,11 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "goponex-sizes":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no layer-list models (llama.cpp graphs only)"}))
+            return 0
+        return goponex_workload(args)
     arch, ftype, n_prompt, batch = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -110,6 +110,46 @@ def tensor_shapes(cfg: dict) -> Dict[str, Tuple[int, ...]]:
     return out
 
 
+def synthetic(width: int, n_heads: int, n_kv: int, ff: int, vocab: int, pattern: str = "mppm", seed: int = 0):
+    """A random-weight model of realistic layer sizes, in memory (timing only): `pattern` lists the layers, "m" = mLSTM
+    without feed-forward, "p" = attention + scan with feed-forward. Returns (config dict, {name: tensor})."""
+    import numpy as np
+    from .safetensors_file import STensor
+    head = 128
+    left = {"heads": n_heads, "kv_heads": n_kv, "dim": head, "vdim": head,
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 8192, "slow": 1.0}},
+            "mask": {"size": 1024, "keep_first": 4}, "scale": head ** -0.5}
+    right = {"inner": 2 * width, "state": 16, "dt_rank": max(16, width // 16), "conv": 4}
+    mm = {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    layers = [{"type": "mlstm", "mixer": mm, "mlp": None} if ch == "m" else
+              {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": ff}} for ch in pattern]
+    cfg = {"architecture": "Goponex", "layers": layers, "norm": {"eps": 1e-5}, "postln_alpha": 1.0, "vocab": vocab, "width": width}
+    rng = np.random.default_rng(seed)
+    tensors = {}
+    for name, shape in tensor_shapes(cfg).items():
+        n = int(np.prod(shape))
+        if len(shape) == 2 and not name.endswith(("conv", "A_log")):
+            a = rng.standard_normal(n, dtype=np.float32) / np.sqrt(shape[1])
+        elif name.endswith("A_log"):
+            a = np.log(rng.uniform(1.0, 16.0, size=n)).astype(np.float32)
+        elif name.endswith("dt.b"):
+            a = np.log(np.expm1(rng.uniform(0.001, 0.1, size=n))).astype(np.float32)
+        elif name.endswith("f.b"):
+            a = rng.uniform(3.0, 6.0, size=n).astype(np.float32)
+        elif name.endswith((".b", "conv")):
+            a = (rng.standard_normal(n, dtype=np.float32) * 0.1)
+        else:
+            a = np.ones(n, dtype=np.float32)
+        bits = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)       # truncation is fine for random weights
+        tensors[name] = STensor(name, "BF16", tuple(shape), bits.reshape(shape))
+    return cfg, tensors
+
+
+def open_synthetic(cfg, tensors, **kw):
+    from .engine import LayeredEngine
+    return LayeredEngine(read_dims(cfg), tensors, **kw)
+
+
 def _open(src, **kw):
     from .engine import LayeredEngine
     dims = read_dims(src.config)

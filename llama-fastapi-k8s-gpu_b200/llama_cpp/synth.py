@@ -54,6 +54,10 @@ ARCHS: Dict[str, Arch] = {
     "llama-3-8b": Arch("llama-3-8b", 32, 4096, 32, 8, 14336, 128256, 500000.0, 1e-5, 8192, "bpe"),
     "mistral-7b": Arch("mistral-7b", 32, 4096, 32, 8, 14336, 32000, 10000.0, 1e-5, 32768, "spm"),
     "llama-3-70b": Arch("llama-3-70b", 80, 8192, 64, 8, 28672, 128256, 500000.0, 1e-5, 8192, "bpe"),
+    # four-layer stacks at three widths: the llama side of the side-by-side timing of the layer-list models (bench.py)
+    "cmp-1k": Arch("cmp-1k", 4, 1024, 8, 2, 4096, 32000, 500000.0, 1e-5, 8192, "bpe"),
+    "cmp-2k": Arch("cmp-2k", 4, 2048, 16, 4, 8192, 32000, 500000.0, 1e-5, 8192, "bpe"),
+    "cmp-4k": Arch("cmp-4k", 4, 4096, 32, 8, 14336, 32000, 500000.0, 1e-5, 8192, "bpe"),
 }
 
 # std of the dequantised values when the block's fp16 scale field(s) are 1.0 and
