@@ -11,6 +11,8 @@
 #include "ptx.cuh"
 #include "quant_blocks.cuh"
 
+#include <algorithm>
+
 namespace b2 {
 
 __device__ __forceinline__ float ld_w(const __nv_bfloat16* w, size_t i) { return __bfloat162float(w[i]); }
@@ -37,12 +39,51 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
     float acc[ROWS_MAX_T];
 #pragma unroll
     for (int t = 0; t < ROWS_MAX_T; t++) acc[t] = 0.f;
-    // lanes take k = lane, lane + 32, ...: neighbouring lanes read neighbouring weights
-    for (int k = lane; k < K; k += 32) {
-        const float wv = ld_w(row, k);
+    // fast path: a lane takes 8 consecutive weights (one 16-byte load for bf16) per step, two steps in flight
+    const bool vec = (K % 8 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+    if (vec) {
+        auto fma8 = [&](const float (&wv)[8], int k) {
 #pragma unroll
-        for (int t = 0; t < ROWS_MAX_T; t++)
-            if (t < T) acc[t] = fmaf(x[(size_t)t * ldx + k], wv, acc[t]);
+            for (int t = 0; t < ROWS_MAX_T; t++)
+                if (t < T) {
+                    const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k);
+                    const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k + 4);
+                    float v = acc[t];
+                    v = fmaf(a.x, wv[0], v); v = fmaf(a.y, wv[1], v); v = fmaf(a.z, wv[2], v); v = fmaf(a.w, wv[3], v);
+                    v = fmaf(b.x, wv[4], v); v = fmaf(b.y, wv[5], v); v = fmaf(b.z, wv[6], v); v = fmaf(b.w, wv[7], v);
+                    acc[t] = v;
+                }
+        };
+        auto load8 = [&](int k, float (&wv)[8]) {
+            if constexpr (sizeof(TW) == 2) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + k));
+                const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) { wv[2 * i] = __uint_as_float(u[i] << 16); wv[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+            } else {
+                const float4 a = __ldg(reinterpret_cast<const float4*>(row + k)), b = __ldg(reinterpret_cast<const float4*>(row + k + 4));
+                wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+            }
+        };
+        int k = lane * 8;
+        for (; k + 256 < K; k += 512) {
+            float w0[8], w1[8];
+            load8(k, w0); load8(k + 256, w1);
+            fma8(w0, k); fma8(w1, k + 256);
+        }
+        for (; k < K; k += 256) {
+            float w0[8];
+            load8(k, w0);
+            fma8(w0, k);
+        }
+    } else {
+        // lanes take k = lane, lane + 32, ...: neighbouring lanes read neighbouring weights
+        for (int k = lane; k < K; k += 32) {
+            const float wv = ld_w(row, k);
+#pragma unroll
+            for (int t = 0; t < ROWS_MAX_T; t++)
+                if (t < T) acc[t] = fmaf(x[(size_t)t * ldx + k], wv, acc[t]);
+        }
     }
 #pragma unroll
     for (int t = 0; t < ROWS_MAX_T; t++) {
@@ -185,6 +226,99 @@ __global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict_
             }
 }
 
+// ---------------------------------------------------------------- tensor cores, large steps: 128 x 128 x 32 tiles, 8 warps of
+// 64 x 32, three stages of 16-byte asynchronous copies, ldmatrix fragments. X is rounded to bf16 ONCE per product by
+// rows_to_bf16_kernel (the 64 x 64 kernel above converts every tile it loads, N / 64 times per element). Needs K % 8 == 0.
+__global__ void rows_to_bf16_kernel(const float* __restrict__ x, int ldx, int T, int K, __nv_bfloat16* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    const long n = (long)T * (K / 2);
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / (K / 2);
+        const int k = (int)(i % (K / 2)) * 2;
+        const float* p = x + t * ldx + k;
+        *reinterpret_cast<__nv_bfloat162*>(y + t * K + k) = __floats2bfloat162_rn(p[0], p[1]);
+    }
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_src) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_src)));
+}
+
+constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 32, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
+constexpr int BIG_SMEM = BIG_STAGES * (BIG_BM + BIG_BN) * BIG_LD * 2;
+__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w,
+                                                            const float* __restrict__ bias, float* __restrict__ y, int ldy,
+                                                            int T, int N, int K, int epi) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ __align__(16) unsigned char big_smem[];
+    __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(big_smem);                       // [stage][BM][LD]
+    __nv_bfloat16* Bs = As + BIG_STAGES * BIG_BM * BIG_LD;                                  // [stage][BN][LD]
+    const int t0 = blockIdx.y * BIG_BM, n0 = blockIdx.x * BIG_BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    const int KT = (K + BIG_BK - 1) / BIG_BK;
+    auto load_stage = [&](int stage, int kt) {
+        const int k0 = kt * BIG_BK;
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            const int c = threadIdx.x + it * 256;          // 512 chunks of 16 bytes per operand tile
+            const int row = c >> 2, kk = (c & 3) * 8;
+            const int k = k0 + kk;
+            const int t = t0 + row, n = n0 + row;
+            const bool ka = k < K;
+            cp_async_16(As + ((size_t)stage * BIG_BM + row) * BIG_LD + kk, xb + (size_t)min(t, T - 1) * K + (ka ? k : 0), (ka && t < T) ? 16 : 0);
+            cp_async_16(Bs + ((size_t)stage * BIG_BN + row) * BIG_LD + kk, w + (size_t)min(n, N - 1) * K + (ka ? k : 0), (ka && n < N) ? 16 : 0);
+        }
+    };
+    float acc[4][4][4] = {};
+    for (int s = 0; s < BIG_STAGES - 1; s++) {
+        if (s < KT) load_stage(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT; kt++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(BIG_STAGES - 2) : "memory");
+        __syncthreads();
+        const int nxt = kt + BIG_STAGES - 1;
+        if (nxt < KT) load_stage(nxt % BIG_STAGES, nxt);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16* A = As + (size_t)(kt % BIG_STAGES) * BIG_BM * BIG_LD;
+        const __nv_bfloat16* B = Bs + (size_t)(kt % BIG_STAGES) * BIG_BN * BIG_LD;
+#pragma unroll
+        for (int ks = 0; ks < BIG_BK; ks += 16) {
+            uint32_t af[4][4], bf[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 4; mi++) ldmatrix_x4(af[mi], A + (size_t)(wm + mi * 16 + (lane & 15)) * BIG_LD + ks + (lane >> 4) * 8);
+#pragma unroll
+            for (int nj = 0; nj < 2; nj++)
+                ldmatrix_x4(bf[nj], B + (size_t)(wn + nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * BIG_LD + ks + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int mi = 0; mi < 4; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 4; ni++) {
+                    const uint32_t b2[2] = {bf[ni >> 1][(ni & 1) * 2], bf[ni >> 1][(ni & 1) * 2 + 1]};
+                    mma_bf16_16816(acc[mi][ni], af[mi], b2);
+                }
+        }
+    }
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int mi = 0; mi < 4; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int t = t0 + wm + mi * 16 + g + (e >> 1) * 8;
+                const int n = n0 + wn + ni * 8 + 2 * tq + (e & 1);
+                if (t < T && n < N) y[(size_t)t * ldy + n] = apply_epi(acc[mi][ni][e], bias, n, epi);
+            }
+}
+
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args&&... args) {
     return launch_chain(k, grid, block, 0, s, std::forward<Args>(args)...);
@@ -198,6 +332,16 @@ cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
         dim3 grid((a.N + 7) / 8), block(256);
         if (wb) return launch_pdl(dense_rows_kernel<__nv_bfloat16>, grid, block, s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
         return launch_pdl(dense_rows_kernel<float>, grid, block, s, a.x, a.ldx, (const float*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    }
+    if (wb && !a.exact && a.xb && a.T >= 64 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) {
+        static bool attr_done = false;
+        if (!attr_done) { cudaFuncSetAttribute(dense_mma_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIG_SMEM); attr_done = true; }
+        const long pairs = (long)a.T * (a.K / 2);
+        cudaError_t ce = launch_chain(rows_to_bf16_kernel, dim3((unsigned)std::min<long>((pairs + 255) / 256, 148 * 8)), dim3(256), 0, s,
+                                      a.x, a.ldx, a.T, a.K, a.xb);
+        if (ce != cudaSuccess) return ce;
+        return launch_chain(dense_mma_big_kernel, dim3((a.N + BIG_BN - 1) / BIG_BN, (a.T + BIG_BM - 1) / BIG_BM), dim3(256), (size_t)BIG_SMEM, s,
+                            (const __nv_bfloat16*)a.xb, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
     }
     dim3 grid((a.N + 63) / 64, (a.T + 63) / 64);
     if (wb && !a.exact)

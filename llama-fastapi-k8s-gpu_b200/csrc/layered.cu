@@ -49,6 +49,7 @@ struct LayeredModel {
     int** block_tables = nullptr;      // device [max_seqs] -> page table
     // step workspace (max_step_tokens rows)
     float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
+    __nv_bfloat16* xb = nullptr;       // a product's input rounded to bf16 [max_step_tokens][widest input]
     int* meta = nullptr;               // device ints: ragged description + wanted rows
     int* meta_host = nullptr;          // pinned
     float* logits_host = nullptr;      // pinned [LOGIT_ROWS][n_vocab]
@@ -238,6 +239,7 @@ int layered_finalize(b2_engine* e) {
     if ((rc = dev_alloc(m, (void**)&m->oL, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->oR, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
+    if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W}) * 2 + 64))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->rows, (size_t)LOGIT_ROWS * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->logits, (size_t)LOGIT_ROWS * V * 4))) return rc;
     const size_t n_meta = (size_t)4 * Tm + 4 * B2_STEP_MAX_ENTRIES + 64;
@@ -375,7 +377,7 @@ static int dense(b2_engine* e, LayeredModel* m, const DenseW& w, const float* x,
     StepProfiler sp(m, e->stream, kind);
     DenseArgs a = {};
     a.x = x; a.ldx = ldx; a.w = w.w; a.w_type = w.type; a.bias = bias; a.y = y; a.ldy = ldy; a.T = T; a.N = w.N; a.K = w.K;
-    a.epi = epi; a.exact = m->exact;
+    a.epi = epi; a.exact = m->exact; a.xb = m->xb;
     CK(dense_launch(a, e->stream));
     e->launches++;
     return B2_OK;

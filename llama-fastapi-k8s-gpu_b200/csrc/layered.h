@@ -37,6 +37,7 @@ struct DenseArgs {
     int T, N, K;
     int epi;
     bool exact;                     // true: 32-bit multiply-adds (no tensor cores, inputs not rounded)
+    __nv_bfloat16* xb;              // scratch [T][K] for X rounded to bf16 (large tensor-core steps); null: not available
 };
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s);
 

@@ -26,6 +26,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {      // all th
     return red[32];
 }
 
+__device__ __forceinline__ void cp_async_4(float* smem_dst, const float* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 0.f ? z + log1pf(expf(-z)) : log1pf(expf(z)); }
@@ -215,8 +221,105 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) window_attn_kernel(WindowAttnA
         a.out[(size_t)t * a.H * a.d + (size_t)h * a.d + d] = o / L;
     }
 }
+// Even head sizes: 8 warps, a warp takes 4 visible keys per round (their loads and the four dot-product reductions overlap),
+// a lane holds pairs of neighbouring entries (one 4- or 8-byte load per key and 64 entries of the head).
+constexpr int ATT2_WARPS = 8, ATT2_KEYS = 4, ATT2_PASS = 4;       // head size <= 256
+template <bool F32>
+__device__ __forceinline__ float2 cache_load2(const void* pool, size_t i) {
+    if constexpr (F32) return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(pool) + i);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(pool) + i);
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+template <bool F32>
+__global__ void __launch_bounds__(ATT2_WARPS * 32) window_attn_pairs_kernel(WindowAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float sm_m[ATT2_WARPS], sm_l[ATT2_WARPS];
+    __shared__ float sm_o[ATT2_WARPS][ATT2_PASS * 64];
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = r.tok_pos[t];
+    const int slot = r.seg_slot[r.tok_seg[t]];
+    const int* table = a.block_tables[slot];
+    const int g = h / (a.H / a.G), d = a.d;
+    const float* q = a.q_rot + (size_t)t * a.H * d + (size_t)h * d;
+    float2 qr[ATT2_PASS], acc[ATT2_PASS];
+#pragma unroll
+    for (int e = 0; e < ATT2_PASS; e++) {
+        const int i = 64 * e + 2 * lane;
+        qr[e] = i < d ? make_float2(q[i] * a.scale, q[i + 1] * a.scale) : make_float2(0.f, 0.f);
+        acc[e] = make_float2(0.f, 0.f);
+    }
+    const int lo = max(0, pos - a.window + 1);
+    const int n_keep = min(a.keep_first, lo);
+    const int n_vis = n_keep + (pos - lo + 1);
+    float m = -INFINITY, l = 0.f;
+    for (int i0 = warp * ATT2_KEYS; i0 < n_vis; i0 += ATT2_WARPS * ATT2_KEYS) {
+        size_t base[ATT2_KEYS];
+        float2 kv[ATT2_KEYS][ATT2_PASS], vv[ATT2_KEYS][ATT2_PASS];
+        float sc[ATT2_KEYS];
+#pragma unroll
+        for (int u = 0; u < ATT2_KEYS; u++) {
+            const int i = min(i0 + u, n_vis - 1);         // past the end: the last key again, its weight is dropped below
+            const int j = i < n_keep ? i : lo + (i - n_keep);
+            base[u] = (((size_t)table[j / a.block_tokens] * a.G + g) * a.block_tokens + j % a.block_tokens) * d;
+        }
+#pragma unroll
+        for (int u = 0; u < ATT2_KEYS; u++)
+#pragma unroll
+            for (int e = 0; e < ATT2_PASS; e++) {
+                const int i = 64 * e + 2 * lane;
+                kv[u][e] = i < d ? cache_load2<F32>(a.k_pool, base[u] + i) : make_float2(0.f, 0.f);
+                vv[u][e] = i < d ? cache_load2<F32>(a.v_pool, base[u] + i) : make_float2(0.f, 0.f);
+            }
+#pragma unroll
+        for (int u = 0; u < ATT2_KEYS; u++) {
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < ATT2_PASS; e++) dot = fmaf(qr[e].x, kv[u][e].x, fmaf(qr[e].y, kv[u][e].y, dot));
+            sc[u] = dot;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < ATT2_KEYS; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+        float m_new = m;
+#pragma unroll
+        for (int u = 0; u < ATT2_KEYS; u++) if (i0 + u < n_vis) m_new = fmaxf(m_new, sc[u]);
+        const float corr = expf(m - m_new);
+        float p[ATT2_KEYS], ps = 0.f;
+#pragma unroll
+        for (int u = 0; u < ATT2_KEYS; u++) { p[u] = i0 + u < n_vis ? expf(sc[u] - m_new) : 0.f; ps += p[u]; }
+        l = l * corr + ps;
+#pragma unroll
+        for (int e = 0; e < ATT2_PASS; e++) {
+            float ax = acc[e].x * corr, ay = acc[e].y * corr;
+#pragma unroll
+            for (int u = 0; u < ATT2_KEYS; u++) { ax = fmaf(p[u], vv[u][e].x, ax); ay = fmaf(p[u], vv[u][e].y, ay); }
+            acc[e] = make_float2(ax, ay);
+        }
+        m = m_new;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < ATT2_PASS; e++) { sm_o[warp][64 * e + 2 * lane] = acc[e].x; sm_o[warp][64 * e + 2 * lane + 1] = acc[e].y; }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w2 = 0; w2 < ATT2_WARPS; w2++) M = fmaxf(M, sm_m[w2]);
+    float L = 0.f;
+    for (int w2 = 0; w2 < ATT2_WARPS; w2++) if (sm_m[w2] > -INFINITY) L += sm_l[w2] * expf(sm_m[w2] - M);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float o = 0.f;
+        for (int w2 = 0; w2 < ATT2_WARPS; w2++) if (sm_m[w2] > -INFINITY) o += sm_o[w2][i] * expf(sm_m[w2] - M);
+        a.out[(size_t)t * a.H * d + (size_t)h * d + i] = o / L;
+    }
+}
+
 cudaError_t window_attn_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.d > ATT_MAXE * 32) return cudaErrorInvalidValue;
+    if (a.d % 2 == 0) {
+        if (a.cache_f32) return launch_chain(window_attn_pairs_kernel<true>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
+        return launch_chain(window_attn_pairs_kernel<false>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
+    }
     return launch_chain(window_attn_kernel, dim3(r.T, a.H), dim3(ATT_WARPS * 32), 0, s, a, r);
 }
 
@@ -291,8 +394,81 @@ __global__ void __launch_bounds__(256) scan_recurrence_kernel(ScanArgs a, Ragged
 #pragma unroll
     for (int e = 0; e < SCAN_MAXS; e++) { const int n = lane + 32 * e; if (n < a.N) sst[n] = S[e]; }
 }
+// Small states (N <= NMAX <= 64): a thread per channel keeps its N states in registers, the step's B and C rows are staged in
+// shared memory for a block of tokens, and the next token's inputs are fetched while the current one is computed. No
+// shuffles, every global access is coalesced over the channels. grid (n_seg, inner / SCAN_CH).
+constexpr int SCAN_CH = 64, SCAN_TB = 16;
+template <int NMAX>
+__global__ void __launch_bounds__(SCAN_CH) scan_recurrence_chan_kernel(ScanArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float bc[];          // [SCAN_TB][2 N]
+    const int seg = blockIdx.x, c = blockIdx.y * SCAN_CH + threadIdx.x;
+    const bool ok = c < a.inner;
+    const int cc = ok ? c : a.inner - 1;    // idle threads shadow the last channel (they still take part in the barriers)
+    const int slot = r.seg_slot[seg], start = r.seg_start[seg], len = r.seg_len[seg];
+    const int hist = a.taps - 1, N = a.N;
+    if (ok) {
+        float* st = a.conv_state + ((size_t)slot * a.inner + c) * hist;
+        for (int k = 0; k < hist; k++) {
+            const int srci = len + k - hist;
+            st[k] = srci >= 0 ? a.proj[(size_t)(start + srci) * a.ldp + a.x_off + c] : st[k + len];
+        }
+    }
+    float A[NMAX], S[NMAX];
+    float* sst = a.ssm_state + ((size_t)slot * a.inner + cc) * N;
+#pragma unroll
+    for (int n = 0; n < NMAX; n++) {
+        A[n] = n < N ? -expf(a.A_log[(size_t)cc * N + n]) : 0.f;
+        S[n] = n < N ? sst[n] : 0.f;
+    }
+    const float Dc = a.D[cc], dtb = a.dt_bias[cc];
+    float n_dt = a.dt_raw[(size_t)start * a.inner + cc], n_x = a.xc[(size_t)start * a.inner + cc];
+    float n_z = a.proj[(size_t)start * a.ldp + a.z_off + cc];
+    for (int i0 = 0; i0 < len; i0 += SCAN_TB) {
+        const int nb = min(SCAN_TB, len - i0);
+        __syncthreads();
+        for (int j = threadIdx.x; j < nb * 2 * N; j += SCAN_CH) {
+            const int tt = j / (2 * N), e = j % (2 * N);
+            bc[j] = a.xproj[(size_t)(start + i0 + tt) * a.ldx + a.R + e];
+        }
+        __syncthreads();
+        for (int ii = 0; ii < nb; ii++) {
+            const int t = start + i0 + ii;
+            const float dt = softplus_f(n_dt + dtb), xv = n_x, zv = n_z;
+            if (i0 + ii + 1 < len) {
+                n_dt = a.dt_raw[(size_t)(t + 1) * a.inner + cc];
+                n_x = a.xc[(size_t)(t + 1) * a.inner + cc];
+                n_z = a.proj[(size_t)(t + 1) * a.ldp + a.z_off + cc];
+            }
+            const float* Bp = bc + ii * 2 * N;
+            const float* Cp = Bp + N;
+            const float dx = dt * xv;
+            float yv = 0.f;
+#pragma unroll
+            for (int n = 0; n < NMAX; n++)
+                if (n < N) {
+                    S[n] = expf(dt * A[n]) * S[n] + dx * Bp[n];
+                    yv = fmaf(S[n], Cp[n], yv);
+                }
+            if (ok) a.y[(size_t)t * a.inner + c] = (yv + Dc * xv) * silu_f(zv);
+        }
+    }
+    if (ok) {
+#pragma unroll
+        for (int n = 0; n < NMAX; n++) if (n < N) sst[n] = S[n];
+    }
+}
+
 cudaError_t scan_recurrence_launch(const ScanArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.N > SCAN_MAXS * 32) return cudaErrorInvalidValue;
+    if (a.N <= 64) {
+        const dim3 grid(r.n_seg, (a.inner + SCAN_CH - 1) / SCAN_CH), block(SCAN_CH);
+        const size_t smem = (size_t)SCAN_TB * 2 * a.N * 4;
+        if (a.N <= 16) return launch_chain(scan_recurrence_chan_kernel<16>, grid, block, smem, s, a, r);
+        if (a.N <= 32) return launch_chain(scan_recurrence_chan_kernel<32>, grid, block, smem, s, a, r);
+        return launch_chain(scan_recurrence_chan_kernel<64>, grid, block, smem, s, a, r);
+    }
     return launch_chain(scan_recurrence_kernel, dim3(r.n_seg, (a.inner + 7) / 8), dim3(256), 0, s, a, r);
 }
 
@@ -326,21 +502,40 @@ __global__ void __launch_bounds__(512) matrix_mem_kernel(MatrixMemArgs a, Ragged
     }
     float m = a.m[(size_t)slot * a.H + h];
     const float qscale = 1.f / sqrtf((float)d);
-    for (int i = 0; i < len; i++) {
-        const int t = start + i, buf = i & 1;
+    // q, k, v of token i + 1 travel to shared memory (asynchronous copies) while token i is computed
+    auto stage = [&](int t, int buf) {
         const float* p = a.proj + (size_t)t * a.ldp;
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            qs[buf * d + j] = p[a.q_off + h * d + j] * qscale;
-            ks[buf * d + j] = p[a.k_off + h * d + j];
+            cp_async_4(&qs[buf * d + j], p + a.q_off + h * d + j);
+            cp_async_4(&ks[buf * d + j], p + a.k_off + h * d + j);
         }
-        if (threadIdx.x < MM_COLS) vs[buf * MM_COLS + threadIdx.x] = col_ok ? p[a.v_off + h * dv + col] : 0.f;
+        if (threadIdx.x < MM_COLS && col_ok) cp_async_4(&vs[buf * MM_COLS + threadIdx.x], p + a.v_off + h * dv + col);
+        cp_async_commit();
+    };
+    if (threadIdx.x < 2 * MM_COLS) vs[threadIdx.x] = 0.f;
+    __syncthreads();
+    float ig_raw = 0.f, fg_raw = 0.f;
+    if (len > 0) {
+        stage(start, 0);
+        ig_raw = a.proj[(size_t)start * a.ldp + a.i_off + h];
+        fg_raw = a.proj[(size_t)start * a.ldp + a.f_off + h];
+    }
+    const float ib_h = a.i_bias[h], fb_h = a.f_bias[h];
+    for (int i = 0; i < len; i++) {
+        const int t = start + i, buf = i & 1;
+        cp_async_wait_all();
+        __syncthreads();
         // gates: capped pre-activations, log-space; every thread computes the same scalars
-        const float ig = a.cap * tanhf((p[a.i_off + h] + a.i_bias[h]) / a.cap);
-        const float fg = log_sigmoid_f(a.cap * tanhf((p[a.f_off + h] + a.f_bias[h]) / a.cap));
+        const float ig = a.cap * tanhf((ig_raw + ib_h) / a.cap);
+        const float fg = log_sigmoid_f(a.cap * tanhf((fg_raw + fb_h) / a.cap));
+        if (i + 1 < len) {
+            stage(t + 1, buf ^ 1);
+            ig_raw = a.proj[(size_t)(t + 1) * a.ldp + a.i_off + h];
+            fg_raw = a.proj[(size_t)(t + 1) * a.ldp + a.f_off + h];
+        }
         const float m_new = fmaxf(fg + m, ig);
         const float da = expf(fg + m - m_new), ib = expf(ig - m_new);
         m = m_new;
-        __syncthreads();
         {
             const float vb = ib * vs[buf * MM_COLS + lc];
             float part = 0.f, npart = 0.f;
@@ -348,7 +543,7 @@ __global__ void __launch_bounds__(512) matrix_mem_kernel(MatrixMemArgs a, Ragged
             for (int k = 0; k < MM_ROWS; k++) {
                 const int row = grp + k * RG;
                 if (row < d) {
-                    const float kk = ks[buf * d + row], qq = qs[buf * d + row];
+                    const float kk = ks[buf * d + row], qq = qs[buf * d + row] * qscale;
                     S[k] = fmaf(da, S[k], kk * vb);
                     nr[k] = fmaf(da, nr[k], ib * kk);
                     part = fmaf(S[k], qq, part);
@@ -365,7 +560,7 @@ __global__ void __launch_bounds__(512) matrix_mem_kernel(MatrixMemArgs a, Ragged
             const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
             a.o_raw[(size_t)t * a.H * dv + (size_t)h * dv + col] = num / den;
         }
-        // the next token stages into the other q/k/v buffer and writes `red` only after its own first barrier
+        // `red` is written again only after the next token's first barrier, which the reading threads reach after their reads
     }
 #pragma unroll
     for (int i = 0; i < MM_ROWS; i++) {

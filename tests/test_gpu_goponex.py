@@ -38,7 +38,8 @@ def run_cut(eng, seqs, key, tokens, cuts):
 
 @pytest.fixture(scope="module")
 def hybrid(native_lib, tmp_path_factory):
-    cfg = gu.config([gu.parallel(mlp=None), gu.mlstm(mlp=96), gu.parallel(mlp=80), gu.mlstm(mlp=None)])
+    cfg = gu.config([gu.parallel(mlp=None), gu.mlstm(mlp=96), gu.parallel(mlp=80, right=gu.scan(inner=36, state=24, dt_rank=4, conv=4)),
+                     gu.mlstm(mlp=None)])
     w = gu.random_weights(cfg, seed=3)
     path = gu.write_model(str(tmp_path_factory.mktemp("goponex_hybrid")), cfg, w)
     return cfg, w, path
@@ -256,13 +257,14 @@ def test_long_decoding(hybrid, dtype):
 
 def test_sizes_that_are_one_or_equal(native_lib, tmp_path):
     """One head, one state, one convolution tap, a window of one token, no kept prefix, full-width rotary without frequency
-    scaling, head sizes that are equal where the other tests have them differ, residual scale 1."""
+    scaling, head sizes that are equal where the other tests have them differ, an odd head size, a state wider than a
+    warp, residual scale 1."""
     from llama_cpp.kv_pages import SequenceSlots
     left = gu.attn(heads=1, kv_heads=1, dim=16, rot=16, window=1, keep=0, scaling=False)
     cfg = gu.config([gu.mlstm(mlp=32, heads=1, dim=16, vdim=16, cap=30.0),
                      gu.parallel(mlp=32, left=left, right=gu.scan(inner=8, state=1, dt_rank=1, conv=1)),
-                     gu.parallel(mlp=None, left=gu.attn(heads=6, kv_heads=1, dim=40, rot=2, window=500, keep=600),
-                                 right=gu.scan(inner=33, state=40, dt_rank=7, conv=6))],
+                     gu.parallel(mlp=None, left=gu.attn(heads=6, kv_heads=1, dim=41, rot=2, window=500, keep=600),
+                                 right=gu.scan(inner=33, state=70, dt_rank=7, conv=6))],
                     width=48, vocab=50, alpha=1.0, eps=1e-5)
     w = gu.random_weights(cfg, seed=8)
     eng = open_engine(gu.write_model(str(tmp_path / "m"), cfg, w), "float32")
