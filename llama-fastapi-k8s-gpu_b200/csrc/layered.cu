@@ -242,7 +242,7 @@ int layered_finalize(b2_engine* e) {
     if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W}) * 2 + 64))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->rows, (size_t)LOGIT_ROWS * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->logits, (size_t)LOGIT_ROWS * V * 4))) return rc;
-    const size_t n_meta = (size_t)4 * Tm + 4 * B2_STEP_MAX_ENTRIES + 64;
+    const size_t n_meta = (size_t)4 * Tm + 2 * (Tm / 64 + B2_STEP_MAX_ENTRIES) + 5 * B2_STEP_MAX_ENTRIES + 64;
     if ((rc = dev_alloc(m, (void**)&m->meta, n_meta * 4))) return rc;
     CK(cudaMallocHost(&m->meta_host, n_meta * 4));
     CK(cudaMallocHost(&m->logits_host, (size_t)LOGIT_ROWS * V * 4));
@@ -494,15 +494,19 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
     CK(cudaSetDevice(c.device));
     cudaStream_t st = e->stream;
     StepChainPdl chain(e->chain_pdl);
-    // ragged description: [tok_id T][tok_seg T][tok_pos T][seg_slot n][seg_start n][seg_len n][seg_pos0 n][rows ...]
+    // ragged description: [tok_id T][tok_seg T][tok_pos T][seg_slot n][seg_start n][seg_len n][seg_pos0 n][tile_seg][tile_row0][rows ...]
     int* h = m->meta_host;
     const int n = n_entries;
     int *h_id = h, *h_seg = h + T, *h_pos = h + 2 * T, *h_slot = h + 3 * T, *h_start = h_slot + n, *h_len = h_start + n, *h_p0 = h_len + n;
-    int* h_rows = h_p0 + n;
-    int row = 0;
+    int n_tiles = 0;
+    for (int i = 0; i < n; i++) n_tiles += (n_tokens[i] + 63) / 64;
+    int *h_tseg = h_p0 + n, *h_trow = h_tseg + n_tiles;
+    int* h_rows = h_trow + n_tiles;
+    int row = 0, tile = 0;
     for (int i = 0; i < n; i++) {
         const int p0 = e->slots[slots[i]].n_past;
         h_slot[i] = slots[i]; h_start[i] = row; h_len[i] = n_tokens[i]; h_p0[i] = p0;
+        for (int k = 0; k < n_tokens[i]; k += 64) { h_tseg[tile] = i; h_trow[tile++] = row + k; }
         for (int k = 0; k < n_tokens[i]; k++, row++) { h_id[row] = tokens[row]; h_seg[row] = i; h_pos[row] = p0 + k; }
     }
     // rows whose logits are needed: the wanted ones, then the last token of every sampled entry
@@ -511,12 +515,13 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
     std::vector<int> samp_row(n, -1);
     for (int i = 0; i < n; i++)
         if (sample && sample[i]) { samp_row[i] = n_rows; h_rows[n_rows++] = h_start[i] + h_len[i] - 1; }
-    const size_t n_meta = (size_t)3 * T + 4 * n + n_rows;
+    const size_t n_meta = (size_t)3 * T + 4 * n + 2 * n_tiles + n_rows;
     CK(cudaMemcpyAsync(m->meta, h, n_meta * 4, cudaMemcpyHostToDevice, st));
     RaggedDev r = {};
     r.tok_id = m->meta; r.tok_seg = m->meta + T; r.tok_pos = m->meta + 2 * T; r.seg_slot = m->meta + 3 * T;
     r.seg_start = r.seg_slot + n; r.seg_len = r.seg_start + n; r.seg_pos0 = r.seg_len + n; r.T = T; r.n_seg = n;
-    const int* d_rows = r.seg_pos0 + n;
+    r.tile_seg = r.seg_pos0 + n; r.tile_row0 = r.tile_seg + n_tiles; r.n_tiles = n_tiles;
+    const int* d_rows = r.tile_row0 + n_tiles;
     if (m->profile) {
         for (auto& pe : m->prof_ev) { cudaEventDestroy(pe.second.first); cudaEventDestroy(pe.second.second); }
         m->prof_ev.clear();

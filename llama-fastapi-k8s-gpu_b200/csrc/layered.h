@@ -22,7 +22,9 @@ struct RaggedDev {             // device pointers, valid for one step
     const int* seg_start;      // [n_seg] first row of the segment
     const int* seg_len;        // [n_seg]
     const int* seg_pos0;       // [n_seg] position of the segment's first token
-    int T, n_seg;
+    const int* tile_seg;       // [n_tiles] tiles of up to 64 consecutive rows of one segment: its segment ...
+    const int* tile_row0;      // ... and its first row
+    int T, n_seg, n_tiles;
 };
 
 // ---------------------------------------------------------------- dense products (dense.cu)

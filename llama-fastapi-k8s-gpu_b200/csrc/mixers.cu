@@ -314,8 +314,178 @@ __global__ void __launch_bounds__(ATT2_WARPS * 32) window_attn_pairs_kernel(Wind
     }
 }
 
+// Tensor-core prompt attention (bf16 pages, head size a multiple of 16 up to 128): a CTA takes one tile of up to 64 consecutive
+// queries of a segment and one head; 4 warps x 16 query rows; keys in blocks of 64 -- first the blocks that hold kept-prefix
+// keys, then the blocks the tile's windows reach -- staged in shared memory once for all 64 queries. S = Q K^T and O += P V
+// with mma.sync m16n8k16 (bf16 in, f32 accumulate); mask, running maximum, exponentials and the sum are 32-bit.
+constexpr int FA_Q = 64, FA_K = 64;
+__device__ __forceinline__ void cp_async_16z(void* smem_dst, const void* gsrc, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int DMAX>
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ __align__(16) unsigned char fa_smem[];
+    const int d = a.d, LD = d + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(fa_smem);     // [64][LD]
+    __nv_bfloat16* Ks = Qs + FA_Q * LD;
+    __nv_bfloat16* Vs = Ks + FA_K * LD;
+    const int tile = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
+    const int nq = min(FA_Q, r.seg_start[seg] + r.seg_len[seg] - row0);
+    const int p0 = r.tok_pos[row0], p_last = p0 + nq - 1;
+    const int* table = a.block_tables[r.seg_slot[seg]];
+    const int g = h / (a.H / a.G);
+    const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(a.k_pool);
+    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(a.v_pool);
+    // queries: scaled, rounded to bf16; rows past the tile are zero
+    for (int i = threadIdx.x; i < FA_Q * (d / 2); i += blockDim.x) {
+        const int rr = i / (d / 2), c = (i % (d / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (rr < nq) {
+            const float* q = a.q_rot + (size_t)(row0 + rr) * a.H * d + (size_t)h * d + c;
+            v = make_float2(q[0] * a.scale, q[1] * a.scale);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(Qs + rr * LD + c) = __floats2bfloat162_rn(v.x, v.y);
+    }
+    const int lo_first = max(0, p0 - a.window + 1);
+    const int n_kept_blocks = lo_first > 0 ? (min(a.keep_first, lo_first) + FA_K - 1) / FA_K : 0;
+    const int win_b0 = max(lo_first / FA_K, n_kept_blocks), win_b1 = p_last / FA_K;
+    const int n_blocks = n_kept_blocks + (win_b1 - win_b0 + 1);
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int gq = lane >> 2, tq = lane & 3;
+    const int qrow[2] = {warp * 16 + gq, warp * 16 + gq + 8};
+    for (int bi = 0; bi < n_blocks; bi++) {
+        const int kb = bi < n_kept_blocks ? bi : win_b0 + (bi - n_kept_blocks);
+        const int j0 = kb * FA_K;
+        __syncthreads();                      // everybody is done with the previous block's K and V (and Q is written)
+        for (int i = threadIdx.x; i < FA_K * (d / 8); i += blockDim.x) {
+            const int rr = i / (d / 8), c = (i % (d / 8)) * 8;
+            const int j = j0 + rr;
+            const int jj = min(j, p_last);
+            const size_t base = (((size_t)table[jj / a.block_tokens] * a.G + g) * a.block_tokens + jj % a.block_tokens) * d + c;
+            cp_async_16z(Ks + rr * LD + c, kp + base, j <= p_last ? 16 : 0);
+            cp_async_16z(Vs + rr * LD + c, vp + base, j <= p_last ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncthreads();
+        // S = Q K^T for this warp's 16 rows
+        float sacc[FA_K / 8][4];
+#pragma unroll
+        for (int ni = 0; ni < FA_K / 8; ni++) sacc[ni][0] = sacc[ni][1] = sacc[ni][2] = sacc[ni][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DMAX; ks += 16) {
+            if (ks < d) {
+                uint32_t af[4];
+                ldsm_x4(af, Qs + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+#pragma unroll
+                for (int nj = 0; nj < FA_K / 16; nj++) {
+                    uint32_t bf[4];
+                    ldsm_x4(bf, Ks + (nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks + ((lane >> 3) & 1) * 8);
+                    mma_16816(sacc[2 * nj], af, bf[0], bf[1]);
+                    mma_16816(sacc[2 * nj + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        // mask, running maximum, exponentials
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int ni = 0; ni < FA_K / 8; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int rr = qrow[e >> 1], i = p0 + rr, j = j0 + ni * 8 + 2 * tq + (e & 1);
+                const bool vis = rr < nq && j <= i && (i - j < a.window || j < a.keep_first);
+                const float v = vis ? sacc[ni][e] : -INFINITY;
+                sacc[ni][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float corr[2], msafe[2];
+#pragma unroll
+        for (int q2 = 0; q2 < 2; q2++) {
+            mx[q2] = fmaxf(mx[q2], __shfl_xor_sync(0xffffffffu, mx[q2], 1));
+            mx[q2] = fmaxf(mx[q2], __shfl_xor_sync(0xffffffffu, mx[q2], 2));
+            const float m_new = fmaxf(m_run[q2], mx[q2]);
+            msafe[q2] = m_new == -INFINITY ? 0.f : m_new;
+            corr[q2] = expf(m_run[q2] - msafe[q2]);
+            m_run[q2] = m_new;
+            l_run[q2] *= corr[q2];
+        }
+#pragma unroll
+        for (int ni = 0; ni < FA_K / 8; ni++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float pv = expf(sacc[ni][e] - msafe[e >> 1]);
+                sacc[ni][e] = pv;
+                l_run[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int i = 0; i < DMAX / 8; i++) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+        // O += P V
+#pragma unroll
+        for (int kc = 0; kc < FA_K / 16; kc++) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(sacc[2 * kc][0], sacc[2 * kc][1]);
+            pf[1] = pack_bf16(sacc[2 * kc][2], sacc[2 * kc][3]);
+            pf[2] = pack_bf16(sacc[2 * kc + 1][0], sacc[2 * kc + 1][1]);
+            pf[3] = pack_bf16(sacc[2 * kc + 1][2], sacc[2 * kc + 1][3]);
+#pragma unroll
+            for (int nd = 0; nd < DMAX / 16; nd++) {
+                if (nd * 16 < d) {
+                    uint32_t vf[4];
+                    ldsm_x4_t(vf, Vs + (kc * 16 + (lane & 15)) * LD + nd * 16 + (lane >> 4) * 8);
+                    mma_16816(o[2 * nd], pf, vf[0], vf[1]);
+                    mma_16816(o[2 * nd + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) {
+        l_run[q2] += __shfl_xor_sync(0xffffffffu, l_run[q2], 1);
+        l_run[q2] += __shfl_xor_sync(0xffffffffu, l_run[q2], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int rr = qrow[e >> 1], c = i * 8 + 2 * tq + (e & 1);
+            if (rr < nq && c < d) a.out[(size_t)(row0 + rr) * a.H * d + (size_t)h * d + c] = o[i][e] / l_run[e >> 1];
+        }
+}
+
 cudaError_t window_attn_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.d > ATT_MAXE * 32) return cudaErrorInvalidValue;
+    if (!a.cache_f32 && r.T > 8 && a.d % 16 == 0 && a.d <= 128) {
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaFuncSetAttribute(window_attn_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (64 + 8) * 2);
+            cudaFuncSetAttribute(window_attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (128 + 8) * 2);
+            attr_done = true;
+        }
+        const size_t smem = (size_t)3 * 64 * (a.d + 8) * 2;
+        if (a.d <= 64) return launch_chain(window_attn_mma_kernel<64>, dim3(r.n_tiles, a.H), dim3(128), smem, s, a, r);
+        return launch_chain(window_attn_mma_kernel<128>, dim3(r.n_tiles, a.H), dim3(128), smem, s, a, r);
+    }
     if (a.d % 2 == 0) {
         if (a.cache_f32) return launch_chain(window_attn_pairs_kernel<true>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
         return launch_chain(window_attn_pairs_kernel<false>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
