@@ -427,7 +427,7 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
             {
                 StepProfiler sp(m, st, 3);
                 CK(scan_recurrence_launch(s, r, st));
-                e->launches++;
+                e->launches += d.d_state <= 32 ? 2 : 1;      // states up to a warp wide: a preparation pass goes first
             }
             if ((rc = dense(e, m, L.scan_o, m->buf[1], d.d_inner, m->oR, W, T))) return rc;
             StepProfiler sp(m, st, 5);
@@ -443,7 +443,7 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
             {
                 StepProfiler sp(m, st, 4);
                 CK(matrix_mem_launch(a, r, st));
-                e->launches += 2;
+                e->launches += 3;
             }
             if ((rc = dense(e, m, L.mm_o, m->buf[1], vd, m->oL, W, T))) return rc;
             StepProfiler sp(m, st, 5);

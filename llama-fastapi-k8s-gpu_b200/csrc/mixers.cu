@@ -9,6 +9,8 @@
 #include "ptx.cuh"
 #include "quant_blocks.cuh"
 
+#include <algorithm>
+
 namespace b2 {
 
 __device__ __forceinline__ float block_sum(float v, float* red) {      // all threads get the sum; red: >= 33 floats
@@ -630,8 +632,95 @@ __global__ void __launch_bounds__(SCAN_CH) scan_recurrence_chan_kernel(ScanArgs 
     }
 }
 
+// States up to a warp wide (N <= LPC <= 32): LPC lanes per channel, one state each, so a step keeps 16-32 times more warps in
+// flight than a thread per channel; the read-out is a shuffle reduction over the LPC lanes. Step sizes and output gates are
+// made beforehand, in place, by scan_prepare_kernel (softplus(dt + bias) over dt_raw, silu over the z columns); inputs are
+// fetched four tokens ahead.
+__global__ void scan_prepare_kernel(ScanArgs a, int T) {
+    griddep_launch();
+    griddep_wait();
+    const long n = (long)T * a.inner;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const long t = i / a.inner;
+        const int c = (int)(i % a.inner);
+        float* dtp = const_cast<float*>(a.dt_raw) + i;
+        *dtp = softplus_f(*dtp + a.dt_bias[c]);
+        float* zp = const_cast<float*>(a.proj) + t * a.ldp + a.z_off + c;
+        *zp = silu_f(*zp);
+    }
+}
+
+template <int LPC>
+__global__ void __launch_bounds__(256) scan_recurrence_lanes_kernel(ScanArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    constexpr int CPB = 256 / LPC, AHEAD = 4;
+    const int seg = blockIdx.x, n = threadIdx.x % LPC, c = blockIdx.y * CPB + threadIdx.x / LPC;
+    const int N = a.N;
+    const bool c_ok = c < a.inner, ok = c_ok && n < N;
+    const int cc = c_ok ? c : a.inner - 1, nn = n < N ? n : 0;
+    const int slot = r.seg_slot[seg], start = r.seg_start[seg], len = r.seg_len[seg];
+    const int hist = a.taps - 1;
+    if (c_ok && n == 0) {
+        float* st = a.conv_state + ((size_t)slot * a.inner + c) * hist;
+        for (int k = 0; k < hist; k++) {
+            const int srci = len + k - hist;
+            st[k] = srci >= 0 ? a.proj[(size_t)(start + srci) * a.ldp + a.x_off + c] : st[k + len];
+        }
+    }
+    float* sst = a.ssm_state + ((size_t)slot * a.inner + cc) * N + nn;
+    const float A = -expf(a.A_log[(size_t)cc * N + nn]);
+    float S = ok ? *sst : 0.f;
+    const float Dc = a.D[cc];
+    struct In { float dt, x, B, C, gate; };
+    auto fetch = [&](int i) {
+        In v;
+        const int t = start + min(i, len - 1);
+        v.dt = a.dt_raw[(size_t)t * a.inner + cc];
+        v.x = a.xc[(size_t)t * a.inner + cc];
+        v.B = ok ? a.xproj[(size_t)t * a.ldx + a.R + nn] : 0.f;
+        v.C = ok ? a.xproj[(size_t)t * a.ldx + a.R + N + nn] : 0.f;
+        v.gate = a.proj[(size_t)t * a.ldp + a.z_off + cc];
+        return v;
+    };
+    In cur[AHEAD], nxt[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; u++) cur[u] = fetch(u);
+    for (int i0 = 0; i0 < len; i0 += AHEAD) {
+        if (i0 + AHEAD < len) {
+#pragma unroll
+            for (int u = 0; u < AHEAD; u++) nxt[u] = fetch(i0 + AHEAD + u);
+        }
+#pragma unroll
+        for (int u = 0; u < AHEAD; u++) {
+            if (i0 + u < len) {
+                const In v = cur[u];
+                S = expf(v.dt * A) * S + v.dt * v.x * v.B;
+                float part = S * v.C;
+#pragma unroll
+                for (int o = LPC / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (n == 0 && c_ok) a.y[(size_t)(start + i0 + u) * a.inner + c] = (part + Dc * v.x) * v.gate;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < AHEAD; u++) cur[u] = nxt[u];
+    }
+    if (ok) *sst = S;
+}
+
 cudaError_t scan_recurrence_launch(const ScanArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.N > SCAN_MAXS * 32) return cudaErrorInvalidValue;
+    if (a.N <= 32) {
+        const long n = (long)r.T * a.inner;
+        cudaError_t ce = launch_chain(scan_prepare_kernel, dim3((unsigned)std::min<long>((n + 255) / 256, 148 * 8)), dim3(256), 0, s, a, r.T);
+        if (ce != cudaSuccess) return ce;
+        const int lpc = a.N <= 4 ? 4 : a.N <= 8 ? 8 : a.N <= 16 ? 16 : 32;
+        const dim3 grid(r.n_seg, (a.inner + 256 / lpc - 1) / (256 / lpc));
+        if (lpc == 4) return launch_chain(scan_recurrence_lanes_kernel<4>, grid, dim3(256), 0, s, a, r);
+        if (lpc == 8) return launch_chain(scan_recurrence_lanes_kernel<8>, grid, dim3(256), 0, s, a, r);
+        if (lpc == 16) return launch_chain(scan_recurrence_lanes_kernel<16>, grid, dim3(256), 0, s, a, r);
+        return launch_chain(scan_recurrence_lanes_kernel<32>, grid, dim3(256), 0, s, a, r);
+    }
     if (a.N <= 64) {
         const dim3 grid(r.n_seg, (a.inner + SCAN_CH - 1) / SCAN_CH), block(SCAN_CH);
         const size_t smem = (size_t)SCAN_TB * 2 * a.N * 4;
@@ -643,103 +732,143 @@ cudaError_t scan_recurrence_launch(const ScanArgs& a, const RaggedDev& r, cudaSt
 }
 
 // ---------------------------------------------------------------- matrix memory (mLSTM)
-// grid (n_seg, H, ceil(dv / 32)): a CTA owns 32 columns of one head's d x dv memory. Thread (col, grp) keeps rows grp, grp + RG,
-// ... of its column in registers (at most MM_ROWS). Per token: stage q, k, v in shared memory, decay + rank-one update,
-// partial read-out per row group, fixed-order sum of the groups. The normaliser n and the running maximum m are carried
-// by every CTA of the head (same arithmetic, same values); the first one writes them back. Two block barriers per token.
-constexpr int MM_ROWS = 16, MM_COLS = 32;      // key size <= 16 * 16 = 256 (512 threads)
+// Gate activations for every (token, head), in place over the projection's i and f columns: i <- cap tanh((i + b_i) / cap),
+// f <- logsigmoid(cap tanh((f + b_f) / cap)). Parallel over the step, so the recurrence below only carries the maximum.
+__global__ void matrix_mem_gates_kernel(MatrixMemArgs a, int T) {
+    griddep_launch();
+    griddep_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * a.H) return;
+    const int t = i / a.H, h = i % a.H;
+    float* p = const_cast<float*>(a.proj) + (size_t)t * a.ldp;
+    p[a.i_off + h] = a.cap * tanhf((p[a.i_off + h] + a.i_bias[h]) / a.cap);
+    p[a.f_off + h] = log_sigmoid_f(a.cap * tanhf((p[a.f_off + h] + a.f_bias[h]) / a.cap));
+}
+
+// grid (n_seg, H, ceil(dv / 32)): a CTA owns 32 columns of one head's d x dv memory. Thread (col, grp) keeps rows grp * MM_ROWS ..
+// of its column in registers; a warp is one row group, and its lanes each carry one row of the normaliser n. Tokens go in blocks of MM_TB: a thread's state update for token t + 1 needs
+// only its own registers after token t, so the block barrier is paid once per block -- for the inputs (q, k, v and the two gate
+// values of the next block arrive in shared memory as asynchronous copies while this block is computed) and for the partial
+// read-outs per row group, which all threads then sum in a fixed order, one (token, column) each. The normaliser n and the
+// running maximum m are carried by every CTA of the head (same arithmetic, same values); the first one writes them back.
+constexpr int MM_ROWS = 16, MM_COLS = 32, MM_TB = 8;      // key size <= 16 * 16 = 256 (512 threads)
 __global__ void __launch_bounds__(512) matrix_mem_kernel(MatrixMemArgs a, RaggedDev r, int RG) {
     griddep_launch();
     griddep_wait();
     extern __shared__ float sm[];
     const int d = a.d, dv = a.dv;
-    float* qs = sm;                    // [2][d]
-    float* ks = qs + 2 * d;            // [2][d]
-    float* vs = ks + 2 * d;            // [2][MM_COLS]
-    float* red = vs + 2 * MM_COLS;     // [RG][MM_COLS + 1]: partial read-outs, last column = partial n.q
+    float* qs = sm;                                // [2][MM_TB][d]
+    float* ks = qs + 2 * MM_TB * d;                // [2][MM_TB][d]
+    float* vs = ks + 2 * MM_TB * d;                // [2][MM_TB][MM_COLS]
+    float* gs = vs + 2 * MM_TB * MM_COLS;          // [2][MM_TB][2]: log input gate, log forget gate
+    float* ms = gs + 2 * MM_TB * 2;                // [2][MM_TB]: running maximum after each token
+    float* red = ms + 2 * MM_TB;                   // [2][MM_TB][RG][MM_COLS + 1]: partial read-outs, last column = partial n.q
+    const int red_tok = RG * (MM_COLS + 1);
     const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * MM_COLS;
     const int slot = r.seg_slot[seg], start = r.seg_start[seg], len = r.seg_len[seg];
     const int lc = threadIdx.x % MM_COLS, grp = threadIdx.x / MM_COLS, col = c0 + lc;
-    const bool col_ok = col < dv;
+    const bool col_ok = col < dv, act = grp < RG;       // threads past the last row group only help with copies and sums
     float* Sg = a.S + (((size_t)slot * a.H + h) * d) * dv;
     float* ng = a.n + ((size_t)slot * a.H + h) * d;
-    float S[MM_ROWS], nr[MM_ROWS];
+    float S[MM_ROWS];
 #pragma unroll
     for (int i = 0; i < MM_ROWS; i++) {
-        const int row = grp + i * RG;
-        S[i] = (col_ok && row < d) ? Sg[(size_t)row * dv + col] : 0.f;
-        nr[i] = row < d ? ng[row] : 0.f;        // every column's thread carries the same copy of its rows of n
+        const int row = grp * MM_ROWS + i;
+        S[i] = (act && col_ok && row < d) ? Sg[(size_t)row * dv + col] : 0.f;
     }
+    const int nrow = grp * MM_ROWS + lc;                      // lanes 0 .. MM_ROWS-1 of a warp: one row of n each
+    const bool n_ok = act && lc < MM_ROWS && nrow < d;
+    float nr = n_ok ? ng[nrow] : 0.f;
+    const bool vec4 = (d % 4) == 0;
     float m = a.m[(size_t)slot * a.H + h];
     const float qscale = 1.f / sqrtf((float)d);
-    // q, k, v of token i + 1 travel to shared memory (asynchronous copies) while token i is computed
-    auto stage = [&](int t, int buf) {
-        const float* p = a.proj + (size_t)t * a.ldp;
-        for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            cp_async_4(&qs[buf * d + j], p + a.q_off + h * d + j);
-            cp_async_4(&ks[buf * d + j], p + a.k_off + h * d + j);
+    auto stage = [&](int i0, int buf) {                  // tokens i0 .. of the segment into buffer `buf`
+        const int nb = min(MM_TB, len - i0);
+        for (int j = threadIdx.x; j < nb * d; j += blockDim.x) {
+            const int u = j / d, e = j % d;
+            const float* p = a.proj + (size_t)(start + i0 + u) * a.ldp;
+            cp_async_4(&qs[(buf * MM_TB + u) * d + e], p + a.q_off + h * d + e);
+            cp_async_4(&ks[(buf * MM_TB + u) * d + e], p + a.k_off + h * d + e);
         }
-        if (threadIdx.x < MM_COLS && col_ok) cp_async_4(&vs[buf * MM_COLS + threadIdx.x], p + a.v_off + h * dv + col);
-        cp_async_commit();
+        for (int j = threadIdx.x; j < nb * MM_COLS; j += blockDim.x) {
+            const int u = j / MM_COLS, e = j % MM_COLS;
+            const float* p = a.proj + (size_t)(start + i0 + u) * a.ldp;
+            if (c0 + e < dv) cp_async_4(&vs[(buf * MM_TB + u) * MM_COLS + e], p + a.v_off + h * dv + c0 + e);
+            if (e < 2) cp_async_4(&gs[(buf * MM_TB + u) * 2 + e], p + (e == 0 ? a.i_off : a.f_off) + h);
+        }
     };
-    if (threadIdx.x < 2 * MM_COLS) vs[threadIdx.x] = 0.f;
+    auto finish = [&](int i0, int buf) {                 // sum of the row groups in a fixed order, then the read-out
+        const int nb = min(MM_TB, len - i0);
+        for (int j = threadIdx.x; j < nb * MM_COLS; j += blockDim.x) {
+            const int u = j / MM_COLS, e = j % MM_COLS;
+            if (c0 + e >= dv) continue;
+            const float* rd = red + (size_t)(buf * MM_TB + u) * red_tok;
+            float num = 0.f, nq = 0.f;
+            for (int g2 = 0; g2 < RG; g2++) { num += rd[g2 * (MM_COLS + 1) + e]; nq += rd[g2 * (MM_COLS + 1) + MM_COLS]; }
+            const float den = fmaxf(fabsf(nq), expf(-ms[buf * MM_TB + u])) + 1e-6f;
+            a.o_raw[(size_t)(start + i0 + u) * a.H * dv + (size_t)h * dv + c0 + e] = num / den;
+        }
+    };
+    for (int j = threadIdx.x; j < 2 * MM_TB * MM_COLS; j += blockDim.x) vs[j] = 0.f;
     __syncthreads();
-    float ig_raw = 0.f, fg_raw = 0.f;
-    if (len > 0) {
-        stage(start, 0);
-        ig_raw = a.proj[(size_t)start * a.ldp + a.i_off + h];
-        fg_raw = a.proj[(size_t)start * a.ldp + a.f_off + h];
-    }
-    const float ib_h = a.i_bias[h], fb_h = a.f_bias[h];
-    for (int i = 0; i < len; i++) {
-        const int t = start + i, buf = i & 1;
+    if (len > 0) stage(0, 0);
+    cp_async_commit();
+    for (int i0 = 0; i0 < len; i0 += MM_TB) {
+        const int nb = min(MM_TB, len - i0), buf = (i0 / MM_TB) & 1;
         cp_async_wait_all();
         __syncthreads();
-        // gates: capped pre-activations, log-space; every thread computes the same scalars
-        const float ig = a.cap * tanhf((ig_raw + ib_h) / a.cap);
-        const float fg = log_sigmoid_f(a.cap * tanhf((fg_raw + fb_h) / a.cap));
-        if (i + 1 < len) {
-            stage(t + 1, buf ^ 1);
-            ig_raw = a.proj[(size_t)(t + 1) * a.ldp + a.i_off + h];
-            fg_raw = a.proj[(size_t)(t + 1) * a.ldp + a.f_off + h];
-        }
-        const float m_new = fmaxf(fg + m, ig);
-        const float da = expf(fg + m - m_new), ib = expf(ig - m_new);
-        m = m_new;
-        {
-            const float vb = ib * vs[buf * MM_COLS + lc];
-            float part = 0.f, npart = 0.f;
+        if (i0 + MM_TB < len) stage(i0 + MM_TB, buf ^ 1);
+        cp_async_commit();
+        if (i0 > 0) finish(i0 - MM_TB, buf ^ 1);
+        for (int u = 0; u < nb; u++) {
+            const int bu = buf * MM_TB + u;
+            const float ig = gs[bu * 2], fg = gs[bu * 2 + 1];
+            const float m_new = fmaxf(fg + m, ig);
+            const float da = expf(fg + m - m_new), ib = expf(ig - m_new);
+            m = m_new;
+            if (threadIdx.x == 0) ms[bu] = m;
+            const float vb = ib * vs[bu * MM_COLS + lc];
+            float part = 0.f;
+            if (act) {
+                const float* kr = ks + bu * d + grp * MM_ROWS;
+                const float* qr = qs + bu * d + grp * MM_ROWS;
+                if (vec4 && grp * MM_ROWS + MM_ROWS <= d) {
 #pragma unroll
-            for (int k = 0; k < MM_ROWS; k++) {
-                const int row = grp + k * RG;
-                if (row < d) {
-                    const float kk = ks[buf * d + row], qq = qs[buf * d + row] * qscale;
-                    S[k] = fmaf(da, S[k], kk * vb);
-                    nr[k] = fmaf(da, nr[k], ib * kk);
-                    part = fmaf(S[k], qq, part);
-                    npart = fmaf(nr[k], qq, npart);
+                    for (int k4 = 0; k4 < MM_ROWS; k4 += 4) {
+                        const float4 k4v = *reinterpret_cast<const float4*>(kr + k4), q4v = *reinterpret_cast<const float4*>(qr + k4);
+                        S[k4 + 0] = fmaf(da, S[k4 + 0], k4v.x * vb); part = fmaf(S[k4 + 0], q4v.x, part);
+                        S[k4 + 1] = fmaf(da, S[k4 + 1], k4v.y * vb); part = fmaf(S[k4 + 1], q4v.y, part);
+                        S[k4 + 2] = fmaf(da, S[k4 + 2], k4v.z * vb); part = fmaf(S[k4 + 2], q4v.z, part);
+                        S[k4 + 3] = fmaf(da, S[k4 + 3], k4v.w * vb); part = fmaf(S[k4 + 3], q4v.w, part);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < MM_ROWS; k++)
+                        if (grp * MM_ROWS + k < d) { S[k] = fmaf(da, S[k], kr[k] * vb); part = fmaf(S[k], qr[k], part); }
                 }
             }
-            red[grp * (MM_COLS + 1) + lc] = part;
-            if (lc == 0) red[grp * (MM_COLS + 1) + MM_COLS] = npart;
+            part *= qscale;
+            // normaliser: lane l of the warp has row l of this group; n . q summed over the group's lanes
+            float npart = 0.f;
+            if (n_ok) { nr = fmaf(da, nr, ib * ks[bu * d + nrow]); npart = nr * qs[bu * d + nrow]; }
+#pragma unroll
+            for (int o = MM_ROWS / 2; o > 0; o >>= 1) npart += __shfl_xor_sync(0xffffffffu, npart, o);
+            npart *= qscale;
+            if (act) {
+                float* rd = red + (size_t)bu * red_tok;
+                rd[grp * (MM_COLS + 1) + lc] = part;
+                if (lc == 0) rd[grp * (MM_COLS + 1) + MM_COLS] = npart;
+            }
         }
-        __syncthreads();
-        if (threadIdx.x < MM_COLS && col_ok) {
-            float num = 0.f, nq = 0.f;
-            for (int g2 = 0; g2 < RG; g2++) { num += red[g2 * (MM_COLS + 1) + lc]; nq += red[g2 * (MM_COLS + 1) + MM_COLS]; }
-            const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
-            a.o_raw[(size_t)t * a.H * dv + (size_t)h * dv + col] = num / den;
-        }
-        // `red` is written again only after the next token's first barrier, which the reading threads reach after their reads
     }
+    __syncthreads();
+    if (len > 0) { const int last0 = (len - 1) / MM_TB * MM_TB; finish(last0, (last0 / MM_TB) & 1); }
 #pragma unroll
     for (int i = 0; i < MM_ROWS; i++) {
-        const int row = grp + i * RG;
-        if (row < d) {
-            if (col_ok) Sg[(size_t)row * dv + col] = S[i];
-            if (lc == 0 && blockIdx.z == 0) ng[row] = nr[i];
-        }
+        const int row = grp * MM_ROWS + i;
+        if (act && col_ok && row < d) Sg[(size_t)row * dv + col] = S[i];
     }
+    if (n_ok && blockIdx.z == 0) ng[nrow] = nr;
     if (threadIdx.x == 0 && blockIdx.z == 0) a.m[(size_t)slot * a.H + h] = m;
 }
 
@@ -762,8 +891,12 @@ __global__ void __launch_bounds__(128) matrix_mem_out_kernel(MatrixMemArgs a) {
 cudaError_t matrix_mem_launch(const MatrixMemArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.dv <= 0 || a.d <= 0 || a.d > MM_ROWS * 16) return cudaErrorInvalidValue;
     const int RG = (a.d + MM_ROWS - 1) / MM_ROWS;
-    const size_t smem = (size_t)(4 * a.d + 2 * MM_COLS + RG * (MM_COLS + 1)) * 4;
-    cudaError_t ce = launch_chain(matrix_mem_kernel, dim3(r.n_seg, a.H, (a.dv + MM_COLS - 1) / MM_COLS), dim3(RG * MM_COLS), smem, s, a, r, RG);
+    const size_t smem = (size_t)(2 * MM_TB * (2 * a.d + MM_COLS + 2 + 1 + RG * (MM_COLS + 1))) * 4;
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(matrix_mem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_done = true; }
+    cudaError_t ce = launch_chain(matrix_mem_gates_kernel, dim3((r.T * a.H + 127) / 128), dim3(128), 0, s, a, r.T);
+    if (ce != cudaSuccess) return ce;
+    ce = launch_chain(matrix_mem_kernel, dim3(r.n_seg, a.H, (a.dv + MM_COLS - 1) / MM_COLS), dim3(std::max(RG * MM_COLS, 64)), smem, s, a, r, RG);
     if (ce != cudaSuccess) return ce;
     return launch_chain(matrix_mem_out_kernel, dim3(r.T, a.H), dim3(128), 0, s, a);
 }

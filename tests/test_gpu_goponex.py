@@ -53,7 +53,7 @@ def tokens_for(cfg, n, seed):
 @pytest.mark.parametrize("layer", ["parallel", "parallel_mlp", "mlstm", "mlstm_mlp"])
 def test_each_mixer_alone(native_lib, tmp_path, layer, dtype):
     from llama_cpp.kv_pages import SequenceSlots
-    L = {"parallel": gu.parallel(), "parallel_mlp": gu.parallel(mlp=100), "mlstm": gu.mlstm(), "mlstm_mlp": gu.mlstm(mlp=64)}[layer]
+    L = {"parallel": gu.parallel(), "parallel_mlp": gu.parallel(mlp=100, right=gu.scan(inner=24, state=40, dt_rank=3, conv=2)), "mlstm": gu.mlstm(), "mlstm_mlp": gu.mlstm(mlp=64)}[layer]
     cfg = gu.config([L])
     w = gu.random_weights(cfg, seed=11)
     eng = open_engine(gu.write_model(str(tmp_path / "m"), cfg, w), dtype)
