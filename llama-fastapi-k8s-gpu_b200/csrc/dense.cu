@@ -25,8 +25,10 @@ __device__ __forceinline__ float apply_epi(float v, const float* bias, int n, in
 }
 
 // ---------------------------------------------------------------- few tokens: a warp per weight row
+// TT = compiled token count (1, 2, 4 or 8 >= T). Fast path (K % 8 == 0, 16-byte aligned rows): a lane takes 8 consecutive
+// weights per load, four loads in flight, so a warp keeps 2 KB of its row on the wire.
 constexpr int ROWS_MAX_T = 8;
-template <typename TW>
+template <typename TW, int TT>
 __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
                                                          const float* __restrict__ bias, float* __restrict__ y, int ldy,
                                                          int T, int N, int K, int epi) {
@@ -36,15 +38,14 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
     const int n = blockIdx.x * 8 + warp;
     if (n >= N) return;
     const TW* row = w + (size_t)n * K;
-    float acc[ROWS_MAX_T];
+    float acc[TT];
 #pragma unroll
-    for (int t = 0; t < ROWS_MAX_T; t++) acc[t] = 0.f;
-    // fast path: a lane takes 8 consecutive weights (one 16-byte load for bf16) per step, two steps in flight
+    for (int t = 0; t < TT; t++) acc[t] = 0.f;
     const bool vec = (K % 8 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
     if (vec) {
         auto fma8 = [&](const float (&wv)[8], int k) {
 #pragma unroll
-            for (int t = 0; t < ROWS_MAX_T; t++)
+            for (int t = 0; t < TT; t++)
                 if (t < T) {
                     const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k);
                     const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k + 4);
@@ -56,20 +57,20 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
         };
         auto load8 = [&](int k, float (&wv)[8]) {
             if constexpr (sizeof(TW) == 2) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + k));
+                const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(row + k));       // streamed once: do not keep in L1
                 const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int i = 0; i < 4; i++) { wv[2 * i] = __uint_as_float(u[i] << 16); wv[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
             } else {
-                const float4 a = __ldg(reinterpret_cast<const float4*>(row + k)), b = __ldg(reinterpret_cast<const float4*>(row + k + 4));
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(row + k)), b = __ldcs(reinterpret_cast<const float4*>(row + k + 4));
                 wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
             }
         };
         int k = lane * 8;
-        for (; k + 256 < K; k += 512) {
-            float w0[8], w1[8];
-            load8(k, w0); load8(k + 256, w1);
-            fma8(w0, k); fma8(w1, k + 256);
+        for (; k + 768 < K; k += 1024) {
+            float w0[8], w1[8], w2[8], w3[8];
+            load8(k, w0); load8(k + 256, w1); load8(k + 512, w2); load8(k + 768, w3);
+            fma8(w0, k); fma8(w1, k + 256); fma8(w2, k + 512); fma8(w3, k + 768);
         }
         for (; k < K; k += 256) {
             float w0[8];
@@ -81,17 +82,27 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
         for (int k = lane; k < K; k += 32) {
             const float wv = ld_w(row, k);
 #pragma unroll
-            for (int t = 0; t < ROWS_MAX_T; t++)
+            for (int t = 0; t < TT; t++)
                 if (t < T) acc[t] = fmaf(x[(size_t)t * ldx + k], wv, acc[t]);
         }
     }
 #pragma unroll
-    for (int t = 0; t < ROWS_MAX_T; t++) {
+    for (int t = 0; t < TT; t++) {
         if (t < T) {
             float v = warp_sum(acc[t]);
             if (lane == 0) y[(size_t)t * ldy + n] = apply_epi(v, bias, n, epi);
         }
     }
+}
+
+template <typename TW>
+static cudaError_t launch_rows(const DenseArgs& a, cudaStream_t s) {
+    dim3 grid((a.N + 7) / 8), block(256);
+    const TW* w = (const TW*)a.w;
+    if (a.T == 1) return launch_chain(dense_rows_kernel<TW, 1>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    if (a.T == 2) return launch_chain(dense_rows_kernel<TW, 2>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    if (a.T <= 4) return launch_chain(dense_rows_kernel<TW, 4>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    return launch_chain(dense_rows_kernel<TW, 8>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
 }
 
 // ---------------------------------------------------------------- exact: 64 x 64 tile, 16-deep, 4 x 4 per thread
@@ -328,11 +339,7 @@ cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
     if (a.T <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
     if (a.w_type != T_BF16 && a.w_type != T_F32) return cudaErrorInvalidValue;
     const bool wb = a.w_type == T_BF16;
-    if (a.T <= ROWS_MAX_T) {
-        dim3 grid((a.N + 7) / 8), block(256);
-        if (wb) return launch_pdl(dense_rows_kernel<__nv_bfloat16>, grid, block, s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-        return launch_pdl(dense_rows_kernel<float>, grid, block, s, a.x, a.ldx, (const float*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    }
+    if (a.T <= ROWS_MAX_T) return wb ? launch_rows<__nv_bfloat16>(a, s) : launch_rows<float>(a, s);
     if (wb && !a.exact && a.xb && a.T >= 64 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) {
         static bool attr_done = false;
         if (!attr_done) { cudaFuncSetAttribute(dense_mma_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIG_SMEM); attr_done = true; }
