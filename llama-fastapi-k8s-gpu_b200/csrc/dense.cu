@@ -24,38 +24,33 @@ __device__ __forceinline__ float apply_epi(float v, const float* bias, int n, in
     return v;
 }
 
-// ---------------------------------------------------------------- few tokens: a warp per weight row
-// TT = compiled token count (1, 2, 4 or 8 >= T). Fast path (K % 8 == 0, 16-byte aligned rows): a lane takes 8 consecutive
-// weights per load, four loads in flight, so a warp keeps 2 KB of its row on the wire.
+// ---------------------------------------------------------------- few tokens: a warp per R weight rows
+// TT = compiled token count (1, 2, 4 or 8 >= T), R = rows per warp (the activations a lane loads serve R rows: with several
+// tokens the activation loads, not the weights, fill the load pipe). Fast path (K % 8 == 0, 16-byte aligned rows): a lane takes
+// 8 consecutive weights per load and keeps R x U = 4 loads in flight, 2 KB per warp on the wire. Each output is still one sum
+// over k in an order that depends on K alone.
 constexpr int ROWS_MAX_T = 8;
-template <typename TW, int TT>
+template <typename TW, int TT, int R>
 __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
                                                          const float* __restrict__ bias, float* __restrict__ y, int ldy,
                                                          int T, int N, int K, int epi) {
     griddep_launch();
     griddep_wait();
+    constexpr int U = 4 / R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;
-    if (n >= N) return;
-    const TW* row = w + (size_t)n * K;
-    float acc[TT];
+    const int n0 = (blockIdx.x * 8 + warp) * R;
+    if (n0 >= N) return;
+    const TW* rows[R];
 #pragma unroll
-    for (int t = 0; t < TT; t++) acc[t] = 0.f;
+    for (int r = 0; r < R; r++) rows[r] = w + (size_t)min(n0 + r, N - 1) * K;      // past the end: the last row again, not stored
+    float acc[TT][R];
+#pragma unroll
+    for (int t = 0; t < TT; t++)
+#pragma unroll
+        for (int r = 0; r < R; r++) acc[t][r] = 0.f;
     const bool vec = (K % 8 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
     if (vec) {
-        auto fma8 = [&](const float (&wv)[8], int k) {
-#pragma unroll
-            for (int t = 0; t < TT; t++)
-                if (t < T) {
-                    const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k);
-                    const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k + 4);
-                    float v = acc[t];
-                    v = fmaf(a.x, wv[0], v); v = fmaf(a.y, wv[1], v); v = fmaf(a.z, wv[2], v); v = fmaf(a.w, wv[3], v);
-                    v = fmaf(b.x, wv[4], v); v = fmaf(b.y, wv[5], v); v = fmaf(b.z, wv[6], v); v = fmaf(b.w, wv[7], v);
-                    acc[t] = v;
-                }
-        };
-        auto load8 = [&](int k, float (&wv)[8]) {
+        auto load8 = [&](const TW* row, int k, float (&wv)[8]) {
             if constexpr (sizeof(TW) == 2) {
                 const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(row + k));       // streamed once: do not keep in L1
                 const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -66,43 +61,68 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
                 wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
             }
         };
+        auto fma8 = [&](const float (&wv)[R][8], int k) {
+#pragma unroll
+            for (int t = 0; t < TT; t++)
+                if (t < T) {
+                    const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k);
+                    const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + k + 4);
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        float v = acc[t][r];
+                        v = fmaf(a.x, wv[r][0], v); v = fmaf(a.y, wv[r][1], v); v = fmaf(a.z, wv[r][2], v); v = fmaf(a.w, wv[r][3], v);
+                        v = fmaf(b.x, wv[r][4], v); v = fmaf(b.y, wv[r][5], v); v = fmaf(b.z, wv[r][6], v); v = fmaf(b.w, wv[r][7], v);
+                        acc[t][r] = v;
+                    }
+                }
+        };
         int k = lane * 8;
-        for (; k + 768 < K; k += 1024) {
-            float w0[8], w1[8], w2[8], w3[8];
-            load8(k, w0); load8(k + 256, w1); load8(k + 512, w2); load8(k + 768, w3);
-            fma8(w0, k); fma8(w1, k + 256); fma8(w2, k + 512); fma8(w3, k + 768);
+        for (; k + (U - 1) * 256 < K; k += U * 256) {
+            float wv[U][R][8];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int r = 0; r < R; r++) load8(rows[r], k + u * 256, wv[u][r]);
+#pragma unroll
+            for (int u = 0; u < U; u++) fma8(wv[u], k + u * 256);
         }
         for (; k < K; k += 256) {
-            float w0[8];
-            load8(k, w0);
-            fma8(w0, k);
+            float wv[R][8];
+#pragma unroll
+            for (int r = 0; r < R; r++) load8(rows[r], k, wv[r]);
+            fma8(wv, k);
         }
     } else {
         // lanes take k = lane, lane + 32, ...: neighbouring lanes read neighbouring weights
         for (int k = lane; k < K; k += 32) {
-            const float wv = ld_w(row, k);
 #pragma unroll
-            for (int t = 0; t < TT; t++)
-                if (t < T) acc[t] = fmaf(x[(size_t)t * ldx + k], wv, acc[t]);
+            for (int r = 0; r < R; r++) {
+                const float wv = ld_w(rows[r], k);
+#pragma unroll
+                for (int t = 0; t < TT; t++)
+                    if (t < T) acc[t][r] = fmaf(x[(size_t)t * ldx + k], wv, acc[t][r]);
+            }
         }
     }
 #pragma unroll
-    for (int t = 0; t < TT; t++) {
-        if (t < T) {
-            float v = warp_sum(acc[t]);
-            if (lane == 0) y[(size_t)t * ldy + n] = apply_epi(v, bias, n, epi);
+    for (int t = 0; t < TT; t++)
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (t < T) {
+                const float v = warp_sum(acc[t][r]);
+                if (lane == 0 && n0 + r < N) y[(size_t)t * ldy + n0 + r] = apply_epi(v, bias, n0 + r, epi);
+            }
         }
-    }
 }
 
 template <typename TW>
 static cudaError_t launch_rows(const DenseArgs& a, cudaStream_t s) {
-    dim3 grid((a.N + 7) / 8), block(256);
     const TW* w = (const TW*)a.w;
-    if (a.T == 1) return launch_chain(dense_rows_kernel<TW, 1>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    if (a.T == 2) return launch_chain(dense_rows_kernel<TW, 2>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    if (a.T <= 4) return launch_chain(dense_rows_kernel<TW, 4>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    return launch_chain(dense_rows_kernel<TW, 8>, grid, block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    dim3 block(256);
+    if (a.T == 1) return launch_chain(dense_rows_kernel<TW, 1, 1>, dim3((a.N + 7) / 8), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    if (a.T == 2) return launch_chain(dense_rows_kernel<TW, 2, 2>, dim3((a.N + 15) / 16), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    if (a.T <= 4) return launch_chain(dense_rows_kernel<TW, 4, 4>, dim3((a.N + 31) / 32), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    return launch_chain(dense_rows_kernel<TW, 8, 4>, dim3((a.N + 31) / 32), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
 }
 
 // ---------------------------------------------------------------- exact: 64 x 64 tile, 16-deep, 4 x 4 per thread
