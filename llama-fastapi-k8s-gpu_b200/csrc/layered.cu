@@ -50,6 +50,8 @@ struct LayeredModel {
     // step workspace (max_step_tokens rows)
     float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
     __nv_bfloat16* xb = nullptr;       // a product's input rounded to bf16 [max_step_tokens][widest input]
+    float* attn_split = nullptr;       // few-token steps: partial attention results per key range
+    int attn_split_floats = 0;
     int* meta = nullptr;               // device ints: ragged description + wanted rows
     int* meta_host = nullptr;          // pinned
     float* logits_host = nullptr;      // pinned [LOGIT_ROWS][n_vocab]
@@ -174,7 +176,7 @@ int layered_finalize(b2_engine* e) {
     if ((rc = matrix(e, "head", V, W, m->head))) return rc;
     if ((rc = vec_f32(e, m, "final.norm", W, 1, &m->final_norm))) return rc;
     const size_t cache_esz = m->exact ? 4 : 2;
-    size_t max_proj = 1, max_buf = 1, max_ff = 1;
+    size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0;
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
@@ -208,6 +210,7 @@ int layered_finalize(b2_engine* e) {
             if ((rc = dev_alloc(m, (void**)&L.ssm_state, (size_t)S * d.d_inner * d.d_state * 4, true))) return rc;
             max_proj = std::max<size_t>(max_proj, L.in_proj.N);
             max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)d.d_inner, (size_t)d.dt_rank + 2 * d.d_state});
+            max_attn = 1; max_attn_d = std::max<size_t>(max_attn_d, d.head_dim);
         } else {
             const std::string a = p + "mix.";
             const int qd = d.mm_heads * d.mm_dim, vd = d.mm_heads * d.mm_vdim;
@@ -240,6 +243,10 @@ int layered_finalize(b2_engine* e) {
     if ((rc = dev_alloc(m, (void**)&m->oR, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
     if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W}) * 2 + 64))) return rc;
+    if (max_attn > 0) {
+        m->attn_split_floats = (int)(148 * 2 * (max_attn_d + 2));       // T * H * splits <= 2 * 148 on the split path
+        if ((rc = dev_alloc(m, (void**)&m->attn_split, (size_t)m->attn_split_floats * 4))) return rc;
+    }
     if ((rc = dev_alloc(m, (void**)&m->rows, (size_t)LOGIT_ROWS * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->logits, (size_t)LOGIT_ROWS * V * 4))) return rc;
     const size_t n_meta = (size_t)4 * Tm + 2 * (Tm / 64 + B2_STEP_MAX_ENTRIES) + 5 * B2_STEP_MAX_ENTRIES + 64;
@@ -405,6 +412,7 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
             a.k_pool = L.k_pool; a.v_pool = L.v_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables;
             a.block_tokens = c.kv_block_tokens; a.H = d.n_head; a.G = d.n_head_kv; a.d = d.head_dim; a.window = d.window;
             a.keep_first = d.keep_first; a.scale = (float)d.attn_scale; a.eps = c.norm_eps; a.q_rot = m->buf[0]; a.out = m->buf[1];
+            a.split_scratch = m->attn_split; a.split_capacity = m->attn_split_floats;
             {
                 StepProfiler sp(m, st, 2);
                 CK(window_attn_store_launch(a, r, st));

@@ -73,6 +73,8 @@ struct WindowAttnArgs {
     float scale, eps;
     float* q_rot;              // scratch [T][H*d]
     float* out;                // [T][H*d]
+    float* split_scratch;      // few-token steps: partial (max, sum, output) per key range, [T][H][splits][d + 2]
+    int split_capacity;        // floats in split_scratch
 };
 // norm + rotate q and k, store k (rotated) and v (= k as projected) into the pages
 cudaError_t window_attn_store_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s);

@@ -253,9 +253,12 @@ __global__ void __launch_bounds__(ATT2_WARPS * 32) window_attn_pairs_kernel(Wind
     }
     const int lo = max(0, pos - a.window + 1);
     const int n_keep = min(a.keep_first, lo);
-    const int n_vis = n_keep + (pos - lo + 1);
+    const int n_all = n_keep + (pos - lo + 1);
+    // several CTAs per (token, head) when the step is small: CTA z takes the z-th range of the visible keys
+    const int n_splits = gridDim.z, chunk = (n_all + n_splits - 1) / n_splits;
+    const int i_begin = blockIdx.z * chunk, n_vis = min(n_all, i_begin + chunk);
     float m = -INFINITY, l = 0.f;
-    for (int i0 = warp * ATT2_KEYS; i0 < n_vis; i0 += ATT2_WARPS * ATT2_KEYS) {
+    for (int i0 = i_begin + warp * ATT2_KEYS; i0 < n_vis; i0 += ATT2_WARPS * ATT2_KEYS) {
         size_t base[ATT2_KEYS];
         float2 kv[ATT2_KEYS][ATT2_PASS], vv[ATT2_KEYS][ATT2_PASS];
         float sc[ATT2_KEYS];
@@ -309,9 +312,29 @@ __global__ void __launch_bounds__(ATT2_WARPS * 32) window_attn_pairs_kernel(Wind
     for (int w2 = 0; w2 < ATT2_WARPS; w2++) M = fmaxf(M, sm_m[w2]);
     float L = 0.f;
     for (int w2 = 0; w2 < ATT2_WARPS; w2++) if (sm_m[w2] > -INFINITY) L += sm_l[w2] * expf(sm_m[w2] - M);
+    float* part = n_splits > 1 ? a.split_scratch + (((size_t)t * a.H + h) * n_splits + blockIdx.z) * (d + 2) : nullptr;
+    if (part && threadIdx.x == 0) { part[0] = M; part[1] = L; }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float o = 0.f;
         for (int w2 = 0; w2 < ATT2_WARPS; w2++) if (sm_m[w2] > -INFINITY) o += sm_o[w2][i] * expf(sm_m[w2] - M);
+        if (part) part[2 + i] = o;                         // unnormalised: window_attn_merge_kernel finishes
+        else a.out[(size_t)t * a.H * d + (size_t)h * d + i] = o / L;
+    }
+}
+
+// sum of the key ranges of one (token, head) in range order
+__global__ void __launch_bounds__(128) window_attn_merge_kernel(WindowAttnArgs a, int n_splits) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x, h = blockIdx.y, d = a.d;
+    const float* part = a.split_scratch + ((size_t)t * a.H + h) * n_splits * (d + 2);
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < n_splits; s2++) M = fmaxf(M, part[(size_t)s2 * (d + 2)]);
+    float L = 0.f;
+    for (int s2 = 0; s2 < n_splits; s2++) { const float ms = part[(size_t)s2 * (d + 2)]; if (ms > -INFINITY) L += part[(size_t)s2 * (d + 2) + 1] * expf(ms - M); }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float o = 0.f;
+        for (int s2 = 0; s2 < n_splits; s2++) { const float ms = part[(size_t)s2 * (d + 2)]; if (ms > -INFINITY) o += part[(size_t)s2 * (d + 2) + 2 + i] * expf(ms - M); }
         a.out[(size_t)t * a.H * d + (size_t)h * d + i] = o / L;
     }
 }
@@ -489,8 +512,17 @@ cudaError_t window_attn_launch(const WindowAttnArgs& a, const RaggedDev& r, cuda
         return launch_chain(window_attn_mma_kernel<128>, dim3(r.n_tiles, a.H), dim3(128), smem, s, a, r);
     }
     if (a.d % 2 == 0) {
-        if (a.cache_f32) return launch_chain(window_attn_pairs_kernel<true>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
-        return launch_chain(window_attn_pairs_kernel<false>, dim3(r.T, a.H), dim3(ATT2_WARPS * 32), 0, s, a, r);
+        // a step of a few tokens does not fill the GPU with one CTA per (token, head): split the keys (up to 16 ranges)
+        int splits = 1;
+        if (a.split_scratch && r.T * a.H < 148) {
+            splits = std::min(16, (2 * 148) / (r.T * a.H));
+            while (splits > 1 && (size_t)r.T * a.H * splits * (a.d + 2) > (size_t)a.split_capacity) splits--;
+        }
+        const dim3 grid(r.T, a.H, splits);
+        cudaError_t ce = a.cache_f32 ? launch_chain(window_attn_pairs_kernel<true>, grid, dim3(ATT2_WARPS * 32), 0, s, a, r)
+                                     : launch_chain(window_attn_pairs_kernel<false>, grid, dim3(ATT2_WARPS * 32), 0, s, a, r);
+        if (ce != cudaSuccess || splits == 1) return ce;
+        return launch_chain(window_attn_merge_kernel, dim3(r.T, a.H), dim3(128), 0, s, a, splits);
     }
     return launch_chain(window_attn_kernel, dim3(r.T, a.H), dim3(ATT_WARPS * 32), 0, s, a, r);
 }
