@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict_
             }
 }
 
-// ---------------------------------------------------------------- tensor cores, large steps: 128 x 128 x 32 tiles, 8 warps of
+// ---------------------------------------------------------------- tensor cores, large steps: 128 x 128 x 64 tiles, 8 warps of
 // 64 x 32, three stages of 16-byte asynchronous copies, ldmatrix fragments. X is rounded to bf16 ONCE per product by
 // rows_to_bf16_kernel (the 64 x 64 kernel above converts every tile it loads, N / 64 times per element). Needs K % 8 == 0.
 __global__ void rows_to_bf16_kernel(const float* __restrict__ x, int ldx, int T, int K, __nv_bfloat16* __restrict__ y) {
@@ -280,7 +280,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_s
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_src)));
 }
 
-constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 32, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
+constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 64, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
 constexpr int BIG_SMEM = BIG_STAGES * (BIG_BM + BIG_BN) * BIG_LD * 2;
 __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w,
                                                             const float* __restrict__ bias, float* __restrict__ y, int ldy,
@@ -297,9 +297,9 @@ __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16*
     auto load_stage = [&](int stage, int kt) {
         const int k0 = kt * BIG_BK;
 #pragma unroll
-        for (int it = 0; it < 2; it++) {
-            const int c = threadIdx.x + it * 256;          // 512 chunks of 16 bytes per operand tile
-            const int row = c >> 2, kk = (c & 3) * 8;
+        for (int it = 0; it < BIG_BK / 16; it++) {
+            const int c = threadIdx.x + it * 256;          // 128 rows x BK / 8 chunks of 16 bytes per operand tile
+            const int row = c / (BIG_BK / 8), kk = (c % (BIG_BK / 8)) * 8;
             const int k = k0 + kk;
             const int t = t0 + row, n = n0 + row;
             const bool ka = k < K;
