@@ -117,10 +117,10 @@ def synthetic(width: int, n_heads: int, n_kv: int, ff: int, vocab: int, pattern:
     from .safetensors_file import STensor
     head = 128
     left = {"heads": n_heads, "kv_heads": n_kv, "dim": head, "vdim": head,
-            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 8192, "slow": 1.0}},
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "fast": 16.0, "original": 8192, "slow": 2.0}},
             "mask": {"size": 1024, "keep_first": 4}, "scale": head ** -0.5}
     right = {"inner": 2 * width, "state": 16, "dt_rank": max(16, width // 16), "conv": 4}
-    mm = {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    mm = {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 12.0}
     layers = [{"type": "mlstm", "mixer": mm, "mlp": None} if ch == "m" else
               {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": ff}} for ch in pattern]
     cfg = {"architecture": "Goponex", "layers": layers, "norm": {"eps": 1e-5}, "postln_alpha": 1.0, "vocab": vocab, "width": width}

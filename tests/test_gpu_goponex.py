@@ -232,6 +232,48 @@ def test_far_token_reaches_through_the_kept_prefix_and_the_state(native_lib, tmp
     assert gu.rel_err(got[n - 1], true) < TOL["float32"]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,keep", [(16, 3), (64, 0), (20, 70), (100, 64), (1000, 5), (65, 129)])
+def test_prompt_attention_tiles(native_lib, tmp_path, window, keep, dtype):
+    """Grouped heads with a head size the tensor-core prompt kernel takes: windows narrower and wider than its 64-query tile,
+    kept prefixes of no, one and several key blocks, a 300-token prompt at once and in portions that straddle the tiles."""
+    from llama_cpp.kv_pages import SequenceSlots
+    cfg = gu.config([gu.parallel(mlp=48, left=gu.attn(heads=4, kv_heads=2, dim=32, rot=16, window=window, keep=keep)),
+                     gu.parallel(left=gu.attn(heads=6, kv_heads=2, dim=48, rot=48, window=window, keep=keep, scaling=False))], width=64)
+    w = gu.random_weights(cfg, seed=13)
+    eng = open_engine(gu.write_model(str(tmp_path / "m"), cfg, w), dtype)
+    toks = tokens_for(cfg, 300, 14)
+    want = ref.forward(cfg, w, toks)
+    seqs = SequenceSlots(eng)
+    whole = run_cut(eng, seqs, "w", toks, [300])
+    parts = run_cut(eng, seqs, "p", toks, [100, 7, 64, 129])
+    eng.close()
+    assert gu.rel_err(whole, want) < TOL[dtype]
+    assert gu.rel_err(parts, want) < TOL[dtype]
+
+
+def test_steps_larger_than_the_engine_takes_at_once(hybrid):
+    """A batch above `max_step_tokens` runs as several native steps that cut the entries where needed."""
+    from llama_cpp.kv_pages import SequenceSlots
+    cfg, w, path = hybrid
+    eng = open_engine(path, "float32", max_step_tokens=16)
+    seqs = SequenceSlots(eng)
+    reqs = {"a": tokens_for(cfg, 50, 70), "b": tokens_for(cfg, 3, 71), "c": tokens_for(cfg, 37, 72)}
+    for k in reqs:
+        seqs.open(k)
+    entries = [(seqs.extend(k, len(t)), t) for k, t in reqs.items()]
+    want = [[0, 17, 49], [2], list(range(37))]
+    got, sampled = eng.step(entries, want=want, sample=[True, False, True])
+    eng.close()
+    refs = [ref.forward(cfg, w, t) for t in reqs.values()]
+    expect = np.concatenate([r[wi] for r, wi in zip(refs, want)])
+    assert got.shape == expect.shape and gu.rel_err(got, expect) < TOL["float32"]
+    assert sampled[1] is None
+    for s, r in ((sampled[0], refs[0]), (sampled[2], refs[2])):
+        top = np.sort(r[-1])[-2:]
+        assert top[1] - top[0] < 1e-3 or s == int(np.argmax(r[-1]))
+
+
 def test_first_tokens(hybrid):
     from llama_cpp.kv_pages import SequenceSlots
     cfg, w, path = hybrid
