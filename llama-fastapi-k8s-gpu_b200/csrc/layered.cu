@@ -39,6 +39,8 @@ struct LyLayer {
     float *up_b = nullptr, *down_b = nullptr;
 };
 
+struct StepGraph { cudaGraphExec_t exec = nullptr; int n_launch = 0; bool failed = false; };
+
 struct LayeredModel {
     b2_layered_config c = {};
     std::vector<LyLayer> layers;
@@ -50,6 +52,8 @@ struct LayeredModel {
     // step workspace (max_step_tokens rows)
     float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
     __nv_bfloat16* xb = nullptr;       // a product's input rounded to bf16 [max_step_tokens][widest input]
+    std::unordered_map<std::string, StepGraph> graphs;     // replayable small steps, by shape (b2_step)
+    bool graphs_on = true;
     float* attn_split = nullptr;       // few-token steps: partial attention results per key range
     int attn_split_floats = 0;
     int* meta = nullptr;               // device ints: ragged description + wanted rows
@@ -271,6 +275,7 @@ void layered_destroy(b2_engine* e) {
     if (m->meta_host) cudaFreeHost(m->meta_host);
     if (m->logits_host) cudaFreeHost(m->logits_host);
     for (auto& pe : m->prof_ev) { cudaEventDestroy(pe.second.first); cudaEventDestroy(pe.second.second); }
+    for (auto& kv : m->graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     delete m;
     e->layered = nullptr;
 }
@@ -331,7 +336,8 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
     m->layers.resize(c->n_layer);
     for (int i = 0; i < c->n_layer; i++) m->layers[i].d = layers[i];
     e->layered = m;
-    e->use_graph = false;
+    e->use_graph = !(c->flags & B2_FLAG_NO_GRAPH) && !getenv("B2_NO_GRAPH");
+    m->graphs_on = e->use_graph;
     e->use_pdl = e->chain_pdl = !(c->flags & B2_FLAG_NO_PDL) && !getenv("B2_NO_CHAIN_PDL");
     auto init = [&]() -> int {
         CK(cudaSetDevice(c->device));
@@ -524,7 +530,6 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
     for (int i = 0; i < n; i++)
         if (sample && sample[i]) { samp_row[i] = n_rows; h_rows[n_rows++] = h_start[i] + h_len[i] - 1; }
     const size_t n_meta = (size_t)3 * T + 4 * n + 2 * n_tiles + n_rows;
-    CK(cudaMemcpyAsync(m->meta, h, n_meta * 4, cudaMemcpyHostToDevice, st));
     RaggedDev r = {};
     r.tok_id = m->meta; r.tok_seg = m->meta + T; r.tok_pos = m->meta + 2 * T; r.seg_slot = m->meta + 3 * T;
     r.seg_start = r.seg_slot + n; r.seg_len = r.seg_start + n; r.seg_pos0 = r.seg_len + n; r.T = T; r.n_seg = n;
@@ -534,30 +539,94 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
         for (auto& pe : m->prof_ev) { cudaEventDestroy(pe.second.first); cudaEventDestroy(pe.second.second); }
         m->prof_ev.clear();
     }
-    int rc = run_layers(e, m, r);
-    if (rc) return rc;
-    m->last_T = T;
     const int W = c.n_embd, V = c.n_vocab;
-    for (int r0 = 0; r0 < n_rows; r0 += LOGIT_ROWS) {
-        const int nr = std::min(LOGIT_ROWS, n_rows - r0);
+    int rc;
+    // logits of rows [r0, r0 + nr): final norm, head, wanted rows to the pinned buffer, sampled rows to their slots
+    auto head_chunk = [&](int r0, int nr) -> int {
         {
             StepProfiler sp(m, st, 5);
             CK(gather_rows_launch(m->x, W, d_rows + r0, nr, m->rows, st));
             CK(layer_norm_launch(m->rows, m->final_norm, c.norm_eps, W, nr, m->rows, st));
             e->launches += 2;
         }
-        if ((rc = dense(e, m, m->head, m->rows, W, m->logits, V, nr, nullptr, EPI_NONE, 6))) return rc;
-        const int n_w = std::max(0, std::min(n_want - r0, nr));       // wanted rows of this chunk go to the host
+        int rc2 = dense(e, m, m->head, m->rows, W, m->logits, V, nr, nullptr, EPI_NONE, 6);
+        if (rc2) return rc2;
+        const int n_w = std::max(0, std::min(n_want - r0, nr));
         if (n_w > 0) CK(cudaMemcpyAsync(m->logits_host, m->logits, (size_t)n_w * V * 4, cudaMemcpyDeviceToHost, st));
         for (int i = 0; i < n; i++)
-            if (samp_row[i] >= r0 && samp_row[i] < r0 + nr) {
-                Slot& s = e->slots[slots[i]];
-                CK(cudaMemcpyAsync(s.logits, m->logits + (size_t)(samp_row[i] - r0) * V, (size_t)V * 4, cudaMemcpyDeviceToDevice, st));
-                s.logits_view = s.logits;
+            if (samp_row[i] >= r0 && samp_row[i] < r0 + nr)
+                CK(cudaMemcpyAsync(e->slots[slots[i]].logits, m->logits + (size_t)(samp_row[i] - r0) * V, (size_t)V * 4, cudaMemcpyDeviceToDevice, st));
+        return B2_OK;
+    };
+    // everything the step enqueues up to the logits, for steps whose rows fit one head chunk
+    auto forward_once = [&]() -> int {
+        CK(cudaMemcpyAsync(m->meta, h, n_meta * 4, cudaMemcpyHostToDevice, st));
+        int rc2 = run_layers(e, m, r);
+        if (rc2) return rc2;
+        return n_rows > 0 ? head_chunk(0, n_rows) : B2_OK;
+    };
+    // Small steps that repeat (the same slots decoding token after token) are replayed as a CUDA graph: the batch description
+    // is read from device memory, so nothing in the launches changes from one such step to the next. A shape is captured the
+    // second time it is seen.
+    bool done = false;
+    if (m->graphs_on && !m->trace && !m->profile && T <= 64 && n_rows <= LOGIT_ROWS) {
+        std::string key;
+        key.reserve(16 + 12 * n);
+        auto put = [&](int v) { key.append(reinterpret_cast<const char*>(&v), sizeof(v)); };
+        put(n); put(n_want);
+        for (int i = 0; i < n; i++) { put(slots[i]); put(n_tokens[i]); put(samp_row[i]); }
+        auto it = m->graphs.find(key);
+        if (it == m->graphs.end()) {
+            if (m->graphs.size() >= 256) {
+                for (auto& kv : m->graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+                m->graphs.clear();
             }
-        if (n_w > 0) {
+            m->graphs[key] = StepGraph();
+        } else {
+            StepGraph& sg = it->second;
+            if (!sg.exec && !sg.failed) {
+                const int64_t before = e->launches;
+                cudaGraph_t g = nullptr;
+                CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+                const int crc = forward_once();
+                const cudaError_t ce = cudaStreamEndCapture(st, &g);
+                sg.n_launch = (int)(e->launches - before);
+                e->launches = before;
+                if (crc == B2_OK && ce == cudaSuccess && g && cudaGraphInstantiate(&sg.exec, g, 0) != cudaSuccess) sg.exec = nullptr;
+                if (g) cudaGraphDestroy(g);
+                if (!sg.exec) { sg.failed = true; cudaGetLastError(); }
+            }
+            if (sg.exec) {
+                CK(cudaGraphLaunch(sg.exec, st));
+                e->launches += sg.n_launch;
+                done = true;
+            }
+        }
+    }
+    if (!done) {
+        if (n_rows <= LOGIT_ROWS) {
+            if ((rc = forward_once())) return rc;
+        } else {
+            CK(cudaMemcpyAsync(m->meta, h, n_meta * 4, cudaMemcpyHostToDevice, st));
+            if ((rc = run_layers(e, m, r))) return rc;
+        }
+    }
+    m->last_T = T;
+    for (int i = 0; i < n; i++) if (samp_row[i] >= 0) e->slots[slots[i]].logits_view = e->slots[slots[i]].logits;
+    if (n_rows <= LOGIT_ROWS) {
+        if (n_want > 0) {
             CK(cudaStreamSynchronize(st));
-            memcpy(host_logits + (size_t)r0 * V, m->logits_host, (size_t)n_w * V * 4);
+            memcpy(host_logits, m->logits_host, (size_t)n_want * V * 4);
+        }
+    } else {
+        for (int r0 = 0; r0 < n_rows; r0 += LOGIT_ROWS) {
+            const int nr = std::min(LOGIT_ROWS, n_rows - r0);
+            if ((rc = head_chunk(r0, nr))) return rc;
+            const int n_w = std::max(0, std::min(n_want - r0, nr));
+            if (n_w > 0) {
+                CK(cudaStreamSynchronize(st));
+                memcpy(host_logits + (size_t)r0 * V, m->logits_host, (size_t)n_w * V * 4);
+            }
         }
     }
     for (int i = 0; i < n; i++) e->slots[slots[i]].n_past += n_tokens[i];

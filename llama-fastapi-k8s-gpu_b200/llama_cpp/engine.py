@@ -284,6 +284,9 @@ class LayeredEngine(EngineBase):
         self.max_step_tokens = int(max_step_tokens or min(max(self.n_ctx, 64), 2048))
         if os.environ.get("B2_NO_PDL"):
             flags |= _cabi.B2_FLAG_NO_PDL
+        if os.environ.get("B2_NO_GRAPH"):
+            flags |= _cabi.B2_FLAG_NO_GRAPH
+        self.flags = flags
         if dtype == "float32":
             flags |= _cabi.B2_FLAG_F32
         cfg = _cabi.B2LayeredConfig(dims.n_layer, dims.n_embd, dims.n_vocab, dims.norm_eps, dims.residual_scale, self.n_ctx,
@@ -383,4 +386,5 @@ class LayeredEngine(EngineBase):
         return {k: dict(ms=ms[i], launches=nl[i]) for i, k in enumerate(kinds)}
 
     def mode(self) -> dict:
-        return dict(graph=False, pdl=not os.environ.get("B2_NO_PDL"), dtype=self.dtype, max_step_tokens=self.max_step_tokens)
+        return dict(graph=not (self.flags & _cabi.B2_FLAG_NO_GRAPH), pdl=not (self.flags & _cabi.B2_FLAG_NO_PDL), dtype=self.dtype,
+                    max_step_tokens=self.max_step_tokens)

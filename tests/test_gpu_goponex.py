@@ -274,6 +274,36 @@ def test_steps_larger_than_the_engine_takes_at_once(hybrid):
         assert top[1] - top[0] < 1e-3 or s == int(np.argmax(r[-1]))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_steps_equal_direct_launches(hybrid, dtype):
+    """Repeating small steps are replayed as CUDA graphs; the logits are bit-identical to launching the kernels directly."""
+    from llama_cpp import _cabi, models
+    from llama_cpp.kv_pages import SequenceSlots
+    cfg, w, path = hybrid
+    toks = {"a": tokens_for(cfg, 60, 80), "b": tokens_for(cfg, 45, 81)}
+    outs = []
+    for flags in (0, _cabi.B2_FLAG_NO_GRAPH):
+        eng = models.open_engine(models.open_model(path), n_ctx=256, max_seqs=2, dtype=dtype, flags=flags)
+        assert eng.mode()["graph"] == (flags == 0)
+        seqs = SequenceSlots(eng)
+        rows = []
+        for k, t in toks.items():
+            seqs.open(k)
+            eng.step([(seqs.extend(k, 5), t[:5])])
+        for i in range(5, 45):
+            lg, _ = eng.step([(seqs.extend(k, 1), [t[i]]) for k, t in toks.items()], want=[[0], [0]])
+            rows.append(lg)
+        for i in range(45, 60):          # one sequence has ended: another shape
+            lg, _ = eng.step([(seqs.extend("a", 1), [toks["a"][i]])], want=[[0]])
+            rows.append(lg)
+        eng.close()
+        outs.append(np.concatenate(rows))
+    assert np.array_equal(outs[0], outs[1])
+    want = np.concatenate([np.stack([ref.forward(cfg, w, t)[i] for t in toks.values()]) for i in range(5, 45)] +
+                          [ref.forward(cfg, w, toks["a"])[45:60]])
+    assert gu.rel_err(outs[0], want) < TOL[dtype]
+
+
 def test_first_tokens(hybrid):
     from llama_cpp.kv_pages import SequenceSlots
     cfg, w, path = hybrid
