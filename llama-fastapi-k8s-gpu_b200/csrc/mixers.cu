@@ -9,6 +9,8 @@
 #include "ptx.cuh"
 #include "quant_blocks.cuh"
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 namespace b2 {
@@ -342,7 +344,9 @@ __global__ void __launch_bounds__(128) window_attn_merge_kernel(WindowAttnArgs a
 // Tensor-core prompt attention (bf16 pages, head size a multiple of 16 up to 128): a CTA takes one tile of up to 64 consecutive
 // queries of a segment and one head; 4 warps x 16 query rows; keys in blocks of 64 -- first the blocks that hold kept-prefix
 // keys, then the blocks the tile's windows reach -- staged in shared memory once for all 64 queries. S = Q K^T and O += P V
-// with mma.sync m16n8k16 (bf16 in, f32 accumulate); mask, running maximum, exponentials and the sum are 32-bit.
+// with mma.sync m16n8k16 (bf16 in, f32 accumulate); mask, running maximum, exponentials and the sum are 32-bit. Queries and
+// probabilities enter the products as TWO bf16 each (value = leading part + remainder), so the only 16-bit rounding on this
+// path is that of the cached keys and values -- the same as on the decode path.
 constexpr int FA_Q = 64, FA_K = 64;
 __device__ __forceinline__ void cp_async_16z(void* smem_dst, const void* gsrc, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
@@ -362,14 +366,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = pack_bf16(a - __low2float(h), b - __high2float(h));
+}
+
 template <int DMAX>
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, RaggedDev r) {
     griddep_launch();
     griddep_wait();
     extern __shared__ __align__(16) unsigned char fa_smem[];
     const int d = a.d, LD = d + 8;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(fa_smem);     // [64][LD]
-    __nv_bfloat16* Ks = Qs + FA_Q * LD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(fa_smem);     // [64][LD] leading bf16 of the scaled query
+    __nv_bfloat16* Ql = Qs + FA_Q * LD;                                 // [64][LD] what the first bf16 leaves over
+    __nv_bfloat16* Ks = Ql + FA_Q * LD;
     __nv_bfloat16* Vs = Ks + FA_K * LD;
     const int tile = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = r.tile_seg[tile], row0 = r.tile_row0[tile];
@@ -387,7 +398,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
             const float* q = a.q_rot + (size_t)(row0 + rr) * a.H * d + (size_t)h * d + c;
             v = make_float2(q[0] * a.scale, q[1] * a.scale);
         }
-        *reinterpret_cast<__nv_bfloat162*>(Qs + rr * LD + c) = __floats2bfloat162_rn(v.x, v.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(Qs + rr * LD + c) = hi;
+        *reinterpret_cast<__nv_bfloat162*>(Ql + rr * LD + c) = __floats2bfloat162_rn(v.x - __low2float(hi), v.y - __high2float(hi));
     }
     const int lo_first = max(0, p0 - a.window + 1);
     const int n_kept_blocks = lo_first > 0 ? (min(a.keep_first, lo_first) + FA_K - 1) / FA_K : 0;
@@ -421,12 +434,15 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
 #pragma unroll
         for (int ks = 0; ks < DMAX; ks += 16) {
             if (ks < d) {
-                uint32_t af[4];
+                uint32_t af[4], al[4];
                 ldsm_x4(af, Qs + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
+                ldsm_x4(al, Ql + (warp * 16 + (lane & 15)) * LD + ks + (lane >> 4) * 8);
 #pragma unroll
                 for (int nj = 0; nj < FA_K / 16; nj++) {
                     uint32_t bf[4];
                     ldsm_x4(bf, Ks + (nj * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + ks + ((lane >> 3) & 1) * 8);
+                    mma_16816(sacc[2 * nj], al, bf[0], bf[1]);
+                    mma_16816(sacc[2 * nj + 1], al, bf[2], bf[3]);
                     mma_16816(sacc[2 * nj], af, bf[0], bf[1]);
                     mma_16816(sacc[2 * nj + 1], af, bf[2], bf[3]);
                 }
@@ -468,16 +484,18 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
         // O += P V
 #pragma unroll
         for (int kc = 0; kc < FA_K / 16; kc++) {
-            uint32_t pf[4];
-            pf[0] = pack_bf16(sacc[2 * kc][0], sacc[2 * kc][1]);
-            pf[1] = pack_bf16(sacc[2 * kc][2], sacc[2 * kc][3]);
-            pf[2] = pack_bf16(sacc[2 * kc + 1][0], sacc[2 * kc + 1][1]);
-            pf[3] = pack_bf16(sacc[2 * kc + 1][2], sacc[2 * kc + 1][3]);
+            uint32_t pf[4], pl[4];         // probabilities as two bf16 each (leading part + remainder): ~16 bits reach the product
+            split_bf16(sacc[2 * kc][0], sacc[2 * kc][1], pf[0], pl[0]);
+            split_bf16(sacc[2 * kc][2], sacc[2 * kc][3], pf[1], pl[1]);
+            split_bf16(sacc[2 * kc + 1][0], sacc[2 * kc + 1][1], pf[2], pl[2]);
+            split_bf16(sacc[2 * kc + 1][2], sacc[2 * kc + 1][3], pf[3], pl[3]);
 #pragma unroll
             for (int nd = 0; nd < DMAX / 16; nd++) {
                 if (nd * 16 < d) {
                     uint32_t vf[4];
                     ldsm_x4_t(vf, Vs + (kc * 16 + (lane & 15)) * LD + nd * 16 + (lane >> 4) * 8);
+                    mma_16816(o[2 * nd], pl, vf[0], vf[1]);
+                    mma_16816(o[2 * nd + 1], pl, vf[2], vf[3]);
                     mma_16816(o[2 * nd], pf, vf[0], vf[1]);
                     mma_16816(o[2 * nd + 1], pf, vf[2], vf[3]);
                 }
@@ -500,14 +518,15 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
 
 cudaError_t window_attn_launch(const WindowAttnArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.d > ATT_MAXE * 32) return cudaErrorInvalidValue;
-    if (!a.cache_f32 && r.T > 8 && a.d % 16 == 0 && a.d <= 128) {
+    static const bool no_mma = getenv("B2_NO_ATTN_MMA") != nullptr;        // tuning aid: scalar attention for prompts too
+    if (!no_mma && !a.cache_f32 && r.T > 8 && a.d % 16 == 0 && a.d <= 128) {
         static bool attr_done = false;
         if (!attr_done) {
-            cudaFuncSetAttribute(window_attn_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (64 + 8) * 2);
-            cudaFuncSetAttribute(window_attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (128 + 8) * 2);
+            cudaFuncSetAttribute(window_attn_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 64 * (64 + 8) * 2);
+            cudaFuncSetAttribute(window_attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 64 * (128 + 8) * 2);
             attr_done = true;
         }
-        const size_t smem = (size_t)3 * 64 * (a.d + 8) * 2;
+        const size_t smem = (size_t)4 * 64 * (a.d + 8) * 2;
         if (a.d <= 64) return launch_chain(window_attn_mma_kernel<64>, dim3(r.n_tiles, a.H), dim3(128), smem, s, a, r);
         return launch_chain(window_attn_mma_kernel<128>, dim3(r.n_tiles, a.H), dim3(128), smem, s, a, r);
     }
