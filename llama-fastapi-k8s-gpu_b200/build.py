@@ -29,6 +29,9 @@ def _newer(target: str, sources) -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    if not os.path.exists(nvcc):
+        import shutil
+        nvcc = shutil.which("nvcc") or nvcc
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "b200_gguf.h")]
     out = os.path.join(LIB, "libb200gguf.so")
     extra = os.environ.get("B2_NVCC_EXTRA", "").split()
