@@ -140,9 +140,18 @@ int b2_synchronize(b2_engine* e);
 #define B2_MIX_WINDOW_SCAN 1     /* sliding-window attention with a kept prefix (values = raw keys) beside a selective
                                     scan (Mamba); the two outputs are RMS-normed over the width and averaged */
 #define B2_MIX_MATRIX_MEMORY 2   /* mLSTM: per-head matrix memory with capped exponential gating */
+#define B2_MIX_LATENT_ATTN 3     /* sliding-window attention over one cached low-rank latent + one shared rotated key part
+                                    per token, per-head softmax sink, sigmoid output gate */
+#define B2_MIX_DELTA_RULE 4      /* gated delta rule: per-head matrix memory with per-row input-dependent decays, short
+                                    causal convolutions on q / k / v */
+#define B2_MIX_SSD 5             /* Mamba-2 state-space recurrence: scalar decay per head, grouped B / C, gated group norm */
+#define B2_FF_RELU2 0            /* squared-ReLU block with biases (when n_ff > 0) */
+#define B2_FF_MOE 1              /* routed mixture of gated (SiLU) experts, n_ff = width of one expert */
+#define B2_BLOCK_POSTSUM_LN 0    /* x <- LayerNorm(alpha * x + f(x)) */
+#define B2_BLOCK_PRENORM_RMS 1   /* x <- x + m * f(RMSNorm(x) * (1 + w)); the embedding and the output are normed the same way */
 typedef struct b2_layer_desc {
     int32_t mixer;            /* B2_MIX_* */
-    int32_t n_ff;             /* width of the squared-ReLU feed-forward block; 0 = the layer has none */
+    int32_t n_ff;             /* width of the feed-forward block (of one expert for B2_FF_MOE); 0 = the layer has none */
     /* window attention */
     int32_t n_head, n_head_kv, head_dim, rot_dims, window, keep_first, rope_orig_ctx, pad0_;
     double attn_scale, rope_base, rope_factor /* <= 0: no frequency blending */, rope_fast, rope_slow;
@@ -151,6 +160,15 @@ typedef struct b2_layer_desc {
     /* matrix memory */
     int32_t mm_heads, mm_dim, mm_vdim, pad_;
     double gate_cap;
+    /* latent attention: n_head, head_dim (unrotated part), window (<= 0: none), attn_scale, rope_base, rot_dims as above */
+    int32_t la_rot_dim, la_vdim, la_rank, ff_kind /* B2_FF_* */;
+    /* delta rule: mm_heads, mm_dim, mm_vdim, conv_taps as above; state-space: mm_heads, mm_vdim, d_state, conv_taps */
+    int32_t key_heads;        /* delta rule: q / k heads; state-space: groups sharing B and C */
+    int32_t rank_a, rank_g;   /* delta rule: inner sizes of the two-step decay and gate projections */
+    int32_t norm_groups;      /* state-space: parts of the gated output norm */
+    /* mixture of experts */
+    int32_t moe_experts, moe_identity, moe_top, moe_groups, moe_keep, pad1_;
+    double moe_scale;
 } b2_layer_desc;
 typedef struct b2_layered_config {
     int32_t n_layer, n_embd, n_vocab;
@@ -160,6 +178,8 @@ typedef struct b2_layered_config {
     int32_t kv_block_tokens, kv_num_blocks;
     int32_t max_step_tokens;  /* most tokens one b2_step call may bring */
     int32_t device, flags;    /* B2_FLAG_F32 */
+    int32_t block_style;      /* B2_BLOCK_* */
+    float logit_scale;        /* logits = head x * logit_scale (0 is read as 1) */
 } b2_layered_config;
 /* Then b2_upload_tensor for every tensor (BF16 / F32), b2_engine_finalize, b2_seq_set_blocks / b2_seq_begin (n_past must be
  * 0: recurrent state cannot be rewound; it zeroes the slot's state) as for any engine. */
@@ -179,7 +199,8 @@ int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const int32_t* n_
 int b2_step_trace(b2_engine* e, int on);
 int b2_step_trace_read(b2_engine* e, float* host_out, int n_layer, int T);
 /* Device time of the last `b2_step` by kernel kind (events around every launch when on != 0; slows the step down).
- * kinds: 0 embed, 1 dense products, 2 attention, 3 scan, 4 matrix memory, 5 norms, 6 head. ms_out[8], launches_out[8]. */
+ * kinds: 0 embed, 1 dense products, 2 attention, 3 scan / state-space, 4 matrix memories, 5 norms, 6 head, 7 expert routing.
+ * ms_out[8], launches_out[8]. */
 int b2_step_profile(b2_engine* e, int on);
 int b2_step_profile_read(b2_engine* e, float* ms_out, int32_t* launches_out);
 

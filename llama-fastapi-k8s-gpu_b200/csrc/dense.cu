@@ -18,10 +18,63 @@ namespace b2 {
 __device__ __forceinline__ float ld_w(const __nv_bfloat16* w, size_t i) { return __bfloat162float(w[i]); }
 __device__ __forceinline__ float ld_w(const float* w, size_t i) { return w[i]; }
 
-__device__ __forceinline__ float apply_epi(float v, const float* bias, int n, int epi) {
-    if (epi != EPI_NONE && bias) v += bias[n];
-    if (epi == EPI_BIAS_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-    return v;
+// what a kernel needs beyond its operands: epilogue, batch strides, grouping (DenseArgs, by value)
+struct DenseDev {
+    const float* x; int ldx;
+    const void* w;
+    const float* bias;
+    float* y; int ldy;
+    int T, N, K, epi;
+    float scale;
+    const float* aux; int ldaux;
+    long x_bs, w_bs, y_bs, aux_bs;
+    int grouped;                   // 0 plain, 1 one pair per blockIdx.y, 2 tiles
+    DenseGroups g;
+};
+
+// The rows [t0, t1) this CTA computes and the operands they use. false: nothing to do.
+template <typename TW>
+__device__ __forceinline__ bool dense_tile(const DenseDev& a, int rows_per_cta, const float*& x, const TW*& w, float*& y, const float*& aux,
+                                           int& t0, int& t1) {
+    x = a.x; w = reinterpret_cast<const TW*>(a.w); y = a.y; aux = a.aux;
+    if (a.grouped == 0) {
+        const long b = blockIdx.z;
+        x += b * a.x_bs; w += b * a.w_bs; y += b * a.y_bs;
+        if (aux) aux += b * a.aux_bs;
+        t0 = blockIdx.y * rows_per_cta; t1 = a.T;
+        return t0 < t1;
+    }
+    if (a.grouped == 1) {
+        const int p = blockIdx.y, g = a.g.group[p];
+        if (g < 0 || g >= a.g.n_groups) return false;
+        w += (long)g * a.g.w_stride;
+        t0 = p; t1 = p + 1;
+        return true;
+    }
+    const int tile = blockIdx.y;
+    if (tile >= *a.g.n_tiles) return false;
+    w += (long)a.g.tile_group[tile] * a.g.w_stride;
+    t0 = a.g.tile_row0[tile]; t1 = t0 + a.g.tile_rows[tile];
+    return true;
+}
+__device__ __forceinline__ int x_row(const DenseDev& a, int t) { return (a.grouped && a.g.x_rows) ? a.g.x_rows[t] : t; }
+
+__device__ __forceinline__ float silu_act(float z) { return z / (1.f + expf(-z)); }
+// one output column
+__device__ __forceinline__ void epi_store(const DenseDev& a, float* y, const float* aux, int t, int n, float v) {
+    if (a.epi == EPI_BIAS || a.epi == EPI_BIAS_RELU2) { if (a.bias) v += a.bias[n]; }
+    if (a.epi == EPI_BIAS_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+    if (a.epi == EPI_MUL_SIGMOID) v *= 1.f / (1.f + expf(-aux[(size_t)t * a.ldaux + n]));
+    y[(size_t)t * a.ldy + n] = v * a.scale;
+}
+// two neighbouring columns n (even) and n + 1
+__device__ __forceinline__ void epi_store2(const DenseDev& a, float* y, const float* aux, int t, int n, float v0, float v1) {
+    if (a.epi == EPI_GLU_SILU) {
+        if (n + 1 < a.N) y[(size_t)t * a.ldy + (n >> 1)] = silu_act(v0) * v1 * a.scale;
+        return;
+    }
+    if (n < a.N) epi_store(a, y, aux, t, n, v0);
+    if (n + 1 < a.N) epi_store(a, y, aux, t, n + 1, v1);
 }
 
 // ---------------------------------------------------------------- few tokens: a warp per R weight rows
@@ -31,15 +84,18 @@ __device__ __forceinline__ float apply_epi(float v, const float* bias, int n, in
 // over k in an order that depends on K alone.
 constexpr int ROWS_MAX_T = 8;
 template <typename TW, int TT, int R>
-__global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
-                                                         const float* __restrict__ bias, float* __restrict__ y, int ldy,
-                                                         int T, int N, int K, int epi) {
+__global__ void __launch_bounds__(256) dense_rows_kernel(DenseDev a) {
     griddep_launch();
     griddep_wait();
     constexpr int U = 4 / R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int N = a.N, K = a.K, ldx = a.ldx;
     const int n0 = (blockIdx.x * 8 + warp) * R;
     if (n0 >= N) return;
+    const float* x; const TW* w; float* y; const float* aux; int t0, t1;
+    if (!dense_tile<TW>(a, ROWS_MAX_T, x, w, y, aux, t0, t1)) return;
+    const int T = a.grouped ? 1 : a.T;
+    if (a.grouped) { x += (size_t)x_row(a, t0) * ldx; y += (size_t)t0 * a.ldy; if (aux) aux += (size_t)t0 * a.ldaux; }
     const TW* rows[R];
 #pragma unroll
     for (int r = 0; r < R; r++) rows[r] = w + (size_t)min(n0 + r, N - 1) * K;      // past the end: the last row again, not stored
@@ -105,44 +161,54 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const float* __restrict
         }
     }
 #pragma unroll
-    for (int t = 0; t < TT; t++)
+    for (int t = 0; t < TT; t++) {
+        if (t >= T) continue;
+        float v[R];
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-            if (t < T) {
-                const float v = warp_sum(acc[t][r]);
-                if (lane == 0 && n0 + r < N) y[(size_t)t * ldy + n0 + r] = apply_epi(v, bias, n0 + r, epi);
-            }
+        for (int r = 0; r < R; r++) v[r] = warp_sum(acc[t][r]);
+        if (lane != 0) continue;
+        if constexpr (R % 2 == 0) {
+#pragma unroll
+            for (int r = 0; r < R; r += 2) epi_store2(a, y, aux, t, n0 + r, v[r], v[r + 1]);
+        } else {
+            epi_store(a, y, aux, t, n0, v[0]);
         }
+    }
 }
 
 template <typename TW>
-static cudaError_t launch_rows(const DenseArgs& a, cudaStream_t s) {
-    const TW* w = (const TW*)a.w;
+static cudaError_t launch_rows(const DenseDev& d, int batch, cudaStream_t s) {
     dim3 block(256);
-    if (a.T == 1) return launch_chain(dense_rows_kernel<TW, 1, 1>, dim3((a.N + 7) / 8), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    if (a.T == 2) return launch_chain(dense_rows_kernel<TW, 2, 2>, dim3((a.N + 15) / 16), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    if (a.T <= 4) return launch_chain(dense_rows_kernel<TW, 4, 4>, dim3((a.N + 31) / 32), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    return launch_chain(dense_rows_kernel<TW, 8, 4>, dim3((a.N + 31) / 32), block, 0, s, a.x, a.ldx, w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    const unsigned gy = d.grouped ? d.T : 1, gz = d.grouped ? 1 : batch;       // grouped: one pair row per blockIdx.y
+    const int N = d.N;
+    if (d.grouped || d.T == 1) {
+        if (d.epi == EPI_GLU_SILU) return launch_chain(dense_rows_kernel<TW, 1, 2>, dim3((N + 15) / 16, gy, gz), block, 0, s, d);
+        return launch_chain(dense_rows_kernel<TW, 1, 1>, dim3((N + 7) / 8, gy, gz), block, 0, s, d);
+    }
+    if (d.T == 2) return launch_chain(dense_rows_kernel<TW, 2, 2>, dim3((N + 15) / 16, gy, gz), block, 0, s, d);
+    if (d.T <= 4) return launch_chain(dense_rows_kernel<TW, 4, 4>, dim3((N + 31) / 32, gy, gz), block, 0, s, d);
+    return launch_chain(dense_rows_kernel<TW, 8, 4>, dim3((N + 31) / 32, gy, gz), block, 0, s, d);
 }
 
 // ---------------------------------------------------------------- exact: 64 x 64 tile, 16-deep, 4 x 4 per thread
 template <typename TW>
-__global__ void __launch_bounds__(256) dense_fma_kernel(const float* __restrict__ x, int ldx, const TW* __restrict__ w,
-                                                        const float* __restrict__ bias, float* __restrict__ y, int ldy,
-                                                        int T, int N, int K, int epi) {
+__global__ void __launch_bounds__(256) dense_fma_kernel(DenseDev a) {
     griddep_launch();
     griddep_wait();
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
-    const int t0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const float* x; const TW* w; float* y; const float* aux; int t0, T;
+    if (!dense_tile<TW>(a, BM, x, w, y, aux, t0, T)) return;
+    const int N = a.N, K = a.K, ldx = a.ldx;
+    const int n0 = blockIdx.x * BN;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // thread tile: rows ty*4.., cols tx*4..
     float acc[4][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
         for (int i = threadIdx.x; i < BM * BK; i += 256) {
             const int r = i / BK, kk = i % BK;
             const int t = t0 + r, k = k0 + kk;
-            xs[kk][r] = (t < T && k < K) ? x[(size_t)t * ldx + k] : 0.f;
+            xs[kk][r] = (t < T && k < K) ? x[(size_t)x_row(a, t) * ldx + k] : 0.f;
             const int n = n0 + r;
             ws[kk][r] = (n < N && k < K) ? ld_w(w, (size_t)n * K + k) : 0.f;
         }
@@ -164,10 +230,7 @@ __global__ void __launch_bounds__(256) dense_fma_kernel(const float* __restrict_
         const int t = t0 + ty * 4 + i;
         if (t >= T) continue;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int n = n0 + tx * 4 + j;
-            if (n < N) y[(size_t)t * ldy + n] = apply_epi(acc[i][j], bias, n, epi);
-        }
+        for (int j = 0; j < 4; j += 2) epi_store2(a, y, aux, t, n0 + tx * 4 + j, acc[i][j], acc[i][j + 1]);
     }
 }
 
@@ -178,15 +241,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
-                                                        const float* __restrict__ bias, float* __restrict__ y, int ldy,
-                                                        int T, int N, int K, int epi) {
+__global__ void __launch_bounds__(128) dense_mma_kernel(DenseDev a) {
     griddep_launch();
     griddep_wait();
     constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;      // rows padded by 16 bytes: fragment reads hit 32 banks
     __shared__ __align__(16) __nv_bfloat16 xs[BM][LD];
     __shared__ __align__(16) __nv_bfloat16 ws[BN][LD];
-    const int t0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const float* x; const __nv_bfloat16* w; float* y; const float* aux; int t0, T;
+    if (!dense_tile<__nv_bfloat16>(a, BM, x, w, y, aux, t0, T)) return;
+    const int N = a.N, K = a.K, ldx = a.ldx;
+    const int n0 = blockIdx.x * BN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
     const int g = lane >> 2, tq = lane & 3;
@@ -199,8 +263,9 @@ __global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict_
             const int t = t0 + r, k = k0 + kk;
             float v0 = 0.f, v1 = 0.f;
             if (t < T) {
-                if (k < K) v0 = x[(size_t)t * ldx + k];
-                if (k + 1 < K) v1 = x[(size_t)t * ldx + k + 1];
+                const float* xr = x + (size_t)x_row(a, t) * ldx;
+                if (k < K) v0 = xr[k];
+                if (k + 1 < K) v1 = xr[k + 1];
             }
             *reinterpret_cast<__nv_bfloat162*>(&xs[r][kk]) = __floats2bfloat162_rn(v0, v1);
         }
@@ -250,10 +315,9 @@ __global__ void __launch_bounds__(128) dense_mma_kernel(const float* __restrict_
 #pragma unroll
         for (int ni = 0; ni < 4; ni++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
+            for (int e = 0; e < 4; e += 2) {
                 const int t = t0 + wm + mi * 16 + g + (e >> 1) * 8;
-                const int n = n0 + wn + ni * 8 + 2 * tq + (e & 1);
-                if (t < T && n < N) y[(size_t)t * ldy + n] = apply_epi(acc[mi][ni][e], bias, n, epi);
+                if (t < T) epi_store2(a, y, aux, t, n0 + wn + ni * 8 + 2 * tq, acc[mi][ni][e], acc[mi][ni][e + 1]);
             }
 }
 
@@ -282,15 +346,23 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_s
 
 constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 64, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
 constexpr int BIG_SMEM = BIG_STAGES * (BIG_BM + BIG_BN) * BIG_LD * 2;
-__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w,
-                                                            const float* __restrict__ bias, float* __restrict__ y, int ldy,
-                                                            int T, int N, int K, int epi) {
+__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, DenseDev a) {
     griddep_launch();
     griddep_wait();
     extern __shared__ __align__(16) unsigned char big_smem[];
     __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(big_smem);                       // [stage][BM][LD]
     __nv_bfloat16* Bs = As + BIG_STAGES * BIG_BM * BIG_LD;                                  // [stage][BN][LD]
-    const int t0 = blockIdx.y * BIG_BM, n0 = blockIdx.x * BIG_BN;
+    const float* x; const __nv_bfloat16* w; float* y; const float* aux; int t0, T;
+    if (!dense_tile<__nv_bfloat16>(a, BIG_BM, x, w, y, aux, t0, T)) return;
+    const int N = a.N, K = a.K;
+    const int n0 = blockIdx.x * BIG_BN;
+    // the rounded copy holds the rows of the step (grouped: of the tokens, gathered here) as [row][K]
+    int my_rows[BIG_BK / 16];
+#pragma unroll
+    for (int it = 0; it < BIG_BK / 16; it++) {
+        const int row = (threadIdx.x + it * 256) / (BIG_BK / 8);
+        my_rows[it] = x_row(a, min(t0 + row, T - 1));
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
     const int KT = (K + BIG_BK - 1) / BIG_BK;
@@ -303,7 +375,7 @@ __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16*
             const int k = k0 + kk;
             const int t = t0 + row, n = n0 + row;
             const bool ka = k < K;
-            cp_async_16(As + ((size_t)stage * BIG_BM + row) * BIG_LD + kk, xb + (size_t)min(t, T - 1) * K + (ka ? k : 0), (ka && t < T) ? 16 : 0);
+            cp_async_16(As + ((size_t)stage * BIG_BM + row) * BIG_LD + kk, xb + (size_t)my_rows[it] * K + (ka ? k : 0), (ka && t < T) ? 16 : 0);
             cp_async_16(Bs + ((size_t)stage * BIG_BN + row) * BIG_LD + kk, w + (size_t)min(n, N - 1) * K + (ka ? k : 0), (ka && n < N) ? 16 : 0);
         }
     };
@@ -343,38 +415,41 @@ __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16*
 #pragma unroll
         for (int ni = 0; ni < 4; ni++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
+            for (int e = 0; e < 4; e += 2) {
                 const int t = t0 + wm + mi * 16 + g + (e >> 1) * 8;
-                const int n = n0 + wn + ni * 8 + 2 * tq + (e & 1);
-                if (t < T && n < N) y[(size_t)t * ldy + n] = apply_epi(acc[mi][ni][e], bias, n, epi);
+                if (t < T) epi_store2(a, y, aux, t, n0 + wn + ni * 8 + 2 * tq, acc[mi][ni][e], acc[mi][ni][e + 1]);
             }
 }
 
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args&&... args) {
-    return launch_chain(k, grid, block, 0, s, std::forward<Args>(args)...);
-}
-
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
-    if (a.T <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+    if (a.T <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return cudaErrorInvalidValue;
     if (a.w_type != T_BF16 && a.w_type != T_F32) return cudaErrorInvalidValue;
+    if (a.epi == EPI_GLU_SILU && a.N % 2) return cudaErrorInvalidValue;
+    if (a.groups && a.batch != 1) return cudaErrorInvalidValue;
     const bool wb = a.w_type == T_BF16;
-    if (a.T <= ROWS_MAX_T) return wb ? launch_rows<__nv_bfloat16>(a, s) : launch_rows<float>(a, s);
-    if (wb && !a.exact && a.xb && a.T >= 64 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) {
+    DenseDev d = {};
+    d.x = a.x; d.ldx = a.ldx; d.w = a.w; d.bias = a.bias; d.y = a.y; d.ldy = a.ldy; d.T = a.T; d.N = a.N; d.K = a.K; d.epi = a.epi;
+    d.scale = a.scale; d.aux = a.aux; d.ldaux = a.ldaux; d.x_bs = a.x_bs; d.w_bs = a.w_bs; d.y_bs = a.y_bs; d.aux_bs = a.aux_bs;
+    if (a.groups) { d.g = *a.groups; d.grouped = a.groups->tile_group ? 2 : 1; }
+    if (d.grouped == 1 || (!d.grouped && a.T <= ROWS_MAX_T)) return wb ? launch_rows<__nv_bfloat16>(d, a.batch, s) : launch_rows<float>(d, a.batch, s);
+    const unsigned gz = d.grouped ? 1 : a.batch;
+    // the large-tile kernel reads a rounded copy of the input rows [T][K]
+    const int x_rows_total = a.T;
+    if (wb && !a.exact && a.xb && a.batch == 1 && !d.grouped && a.T >= 64 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) {
         static bool attr_done = false;
         if (!attr_done) { cudaFuncSetAttribute(dense_mma_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIG_SMEM); attr_done = true; }
-        const long pairs = (long)a.T * (a.K / 2);
+        const long pairs = (long)x_rows_total * (a.K / 2);
         cudaError_t ce = launch_chain(rows_to_bf16_kernel, dim3((unsigned)std::min<long>((pairs + 255) / 256, 148 * 8)), dim3(256), 0, s,
-                                      a.x, a.ldx, a.T, a.K, a.xb);
+                                      a.x, a.ldx, x_rows_total, a.K, a.xb);
         if (ce != cudaSuccess) return ce;
-        return launch_chain(dense_mma_big_kernel, dim3((a.N + BIG_BN - 1) / BIG_BN, (a.T + BIG_BM - 1) / BIG_BM), dim3(256), (size_t)BIG_SMEM, s,
-                            (const __nv_bfloat16*)a.xb, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+        const unsigned gy = d.grouped ? (unsigned)a.groups->max_tiles : (unsigned)((a.T + BIG_BM - 1) / BIG_BM);
+        return launch_chain(dense_mma_big_kernel, dim3((a.N + BIG_BN - 1) / BIG_BN, gy), dim3(256), (size_t)BIG_SMEM, s,
+                            (const __nv_bfloat16*)a.xb, d);
     }
-    dim3 grid((a.N + 63) / 64, (a.T + 63) / 64);
-    if (wb && !a.exact)
-        return launch_pdl(dense_mma_kernel, grid, dim3(128), s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    if (wb) return launch_pdl(dense_fma_kernel<__nv_bfloat16>, grid, dim3(256), s, a.x, a.ldx, (const __nv_bfloat16*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
-    return launch_pdl(dense_fma_kernel<float>, grid, dim3(256), s, a.x, a.ldx, (const float*)a.w, a.bias, a.y, a.ldy, a.T, a.N, a.K, a.epi);
+    dim3 grid((a.N + 63) / 64, d.grouped ? (unsigned)a.groups->max_tiles : (unsigned)((a.T + 63) / 64), gz);
+    if (wb && !a.exact) return launch_chain(dense_mma_kernel, grid, dim3(128), 0, s, d);
+    if (wb) return launch_chain(dense_fma_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, d);
+    return launch_chain(dense_fma_kernel<float>, grid, dim3(256), 0, s, d);
 }
 
 }  // namespace b2

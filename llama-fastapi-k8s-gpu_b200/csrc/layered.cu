@@ -1,7 +1,8 @@
 // Layer-list models (include/b200_gguf.h: b2_engine_create_layered, b2_step): the graph of a decoder given as a list of
-// layers -- window attention beside a selective scan, or an mLSTM matrix memory, each optionally followed by a squared-ReLU
-// feed-forward block, with the layer norm AFTER each residual sum -- over dense bf16 / f32 tensors, stepped over ragged
-// batches. Shares the engine object with the llama graph (engine.cu): tensors, sequence slots and their page tables,
+// layers over dense bf16 / f32 tensors, stepped over ragged batches. Token mixers: window attention beside a selective
+// scan, an mLSTM matrix memory, latent attention, the gated delta rule, a Mamba-2 state-space layer. Feed-forward blocks:
+// squared ReLU with biases, or a routed mixture of gated experts. Two block styles: layer norm AFTER each residual sum, or
+// pre-norm (zero-centred RMS weights) with a scaled branch. Shares the engine object with the llama graph (engine.cu): tensors, sequence slots and their page tables,
 // sampler state, stream, error reporting. Owns: fused projection matrices, per-layer cache pages, per-slot recurrent
 // state, the step workspace.
 #include "engine_state.h"
@@ -37,6 +38,19 @@ struct LyLayer {
     // feed-forward
     DenseW up, down;
     float *up_b = nullptr, *down_b = nullptr;
+    // latent attention: la_proj rows q | dkv | g; uk_t = W_uk transposed per head [H][rank][d]
+    DenseW la_proj, uk_t, uv;
+    int g_off = 0, dkv_off = 0;
+    float *c_norm = nullptr, *sink = nullptr;
+    void* la_pool = nullptr;
+    // delta rule (st_proj rows q | k | v | b | a1 | g1) and state-space layer (st_proj rows z | x | B | C | dt)
+    DenseW st_proj, a2, g2, st_o;
+    int v_off = 0, b_off = 0, a1_off = 0, g1_off = 0, dt_off = 0, conv_off = 0, conv_C = 0;
+    float *st_conv_w = nullptr, *st_conv_b = nullptr, *st_conv_state = nullptr, *st_A_log = nullptr, *st_dt_bias = nullptr,
+          *st_D = nullptr, *st_norm = nullptr, *st_state = nullptr;
+    // mixture of experts: gate_up = [E][2 ff][W] with rows 2i = gate i, 2i + 1 = up i; e_down = [E][W][ff]
+    DenseW router, gate_up, e_down;
+    float* correction = nullptr;
 };
 
 struct StepGraph { cudaGraphExec_t exec = nullptr; int n_launch = 0; bool failed = false; };
@@ -46,14 +60,18 @@ struct LayeredModel {
     std::vector<LyLayer> layers;
     std::vector<void*> owned;          // device allocations freed at destroy
     DenseW embed, head;
-    float* final_norm = nullptr;
+    float *final_norm = nullptr, *embed_norm = nullptr;
     bool exact = false;                // B2_FLAG_F32
     int** block_tables = nullptr;      // device [max_seqs] -> page table
     // step workspace (max_step_tokens rows)
-    float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
+    float *x = nullptr, *proj = nullptr, *buf[4] = {}, *oL = nullptr, *oR = nullptr, *hn = nullptr, *ff = nullptr, *rows = nullptr, *logits = nullptr;
     __nv_bfloat16* xb = nullptr;       // a product's input rounded to bf16 [max_step_tokens][widest input]
     std::unordered_map<std::string, StepGraph> graphs;     // replayable small steps, by shape (b2_step)
     bool graphs_on = true;
+    // mixture of experts: router outputs, choices, the sorted pair table, expert activations and outputs
+    float *moe_logits = nullptr, *moe_weight = nullptr, *moe_h = nullptr, *moe_y = nullptr;
+    int *moe_sel = nullptr, *moe_tok = nullptr, *moe_pos = nullptr, *moe_rows = nullptr, *moe_tiles = nullptr;
+    int moe_max_tiles = 0;
     float* attn_split = nullptr;       // few-token steps: partial attention results per key range
     int attn_split_floats = 0;
     int* meta = nullptr;               // device ints: ragged description + wanted rows
@@ -135,6 +153,58 @@ static int fuse(b2_engine* e, LayeredModel* m, const std::vector<std::pair<std::
     return B2_OK;
 }
 
+// W [H * d][rank] -> [H][rank][d] (elements of esz bytes): the per-head key expansion as a map applied to the query
+__global__ void transpose_heads_kernel(const unsigned char* src, unsigned char* dst, int H, int d, int rank, int esz) {
+    const long n = (long)H * d * rank, i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int c = (int)(i % rank), j = (int)((i / rank) % d), h = (int)(i / ((long)rank * d));
+    const long o = ((long)h * rank + c) * d + j;
+    for (int b = 0; b < esz; b++) dst[o * esz + b] = src[i * esz + b];
+}
+
+// several f32 tables of rows of `cols` entries one after another in one allocation
+static int concat_f32(b2_engine* e, LayeredModel* m, const std::vector<std::pair<std::string, int>>& parts, int cols, float** out) {
+    long rows = 0;
+    for (auto& p : parts) rows += p.second;
+    int rc = dev_alloc(m, (void**)out, (size_t)rows * cols * 4); if (rc) return rc;
+    long at = 0;
+    for (auto& p : parts) {
+        DevTensor t;
+        if ((rc = find(e, p.first, cols, p.second, t))) return rc;
+        const long n = (long)p.second * cols;
+        to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(t.type, t.ptr, n, *out + at);
+        CK(cudaGetLastError());
+        at += n;
+    }
+    return B2_OK;
+}
+
+// the experts of a layer stacked: [E][2 ff][W] with gate and up rows interleaved, and [E][W][ff]
+static int stack_experts(b2_engine* e, LayeredModel* m, const std::string& p, int E, int ff, int W, DenseW& gate_up, DenseW& down) {
+    int type = -1;
+    void *gu = nullptr, *dn = nullptr;
+    for (int x = 0; x < E; x++) {
+        DevTensor tg, tu, td;
+        const std::string q = p + "e" + std::to_string(x) + ".";
+        int rc;
+        if ((rc = find(e, q + "gate", W, ff, tg)) || (rc = find(e, q + "up", W, ff, tu)) || (rc = find(e, q + "down", ff, W, td))) return rc;
+        if (type < 0) {
+            type = tg.type;
+            const size_t esz = type == T_BF16 ? 2 : 4;
+            if ((rc = dev_alloc(m, &gu, (size_t)E * 2 * ff * W * esz + 64)) || (rc = dev_alloc(m, &dn, (size_t)E * W * ff * esz + 64))) return rc;
+        }
+        if (tg.type != type || tu.type != type || td.type != type) return b2_fail(B2_ERR_UNSUPPORTED, q + ": the experts of a layer must share a dtype");
+        const size_t esz = type == T_BF16 ? 2 : 4, rowb = (size_t)W * esz;
+        char* base = (char*)gu + (size_t)x * 2 * ff * rowb;
+        CK(cudaMemcpy2DAsync(base, 2 * rowb, tg.ptr, rowb, rowb, ff, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpy2DAsync(base + rowb, 2 * rowb, tu.ptr, rowb, rowb, ff, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync((char*)dn + (size_t)x * W * ff * esz, td.ptr, (size_t)W * ff * esz, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    gate_up.w = gu; gate_up.type = type; gate_up.N = 2 * ff; gate_up.K = W;
+    down.w = dn; down.type = type; down.N = W; down.K = ff;
+    return B2_OK;
+}
+
 // blended rotary frequencies (interpolated below the slow boundary, original above the fast one, linear ramp between)
 // and the magnitude factor; cos / sin per position in double precision
 static int build_rotary(b2_engine* e, LayeredModel* m, LyLayer& L) {
@@ -179,8 +249,10 @@ int layered_finalize(b2_engine* e) {
     if ((rc = matrix(e, "embed", V, W, m->embed))) return rc;
     if ((rc = matrix(e, "head", V, W, m->head))) return rc;
     if ((rc = vec_f32(e, m, "final.norm", W, 1, &m->final_norm))) return rc;
+    if (c.block_style == B2_BLOCK_PRENORM_RMS && (rc = vec_f32(e, m, "embed.norm", W, 1, &m->embed_norm))) return rc;
     const size_t cache_esz = m->exact ? 4 : 2;
     size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0;
+    size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0;
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
@@ -215,6 +287,68 @@ int layered_finalize(b2_engine* e) {
             max_proj = std::max<size_t>(max_proj, L.in_proj.N);
             max_buf = std::max<size_t>({max_buf, (size_t)qd, (size_t)d.d_inner, (size_t)d.dt_rank + 2 * d.d_state});
             max_attn = 1; max_attn_d = std::max<size_t>(max_attn_d, d.head_dim);
+        } else if (d.mixer == B2_MIX_LATENT_ATTN) {
+            const std::string a = p + "mix.";
+            const int H = d.n_head, dq = d.head_dim + d.la_rot_dim, Dk = d.la_rank + d.la_rot_dim, vd = H * d.la_vdim;
+            std::vector<int> offs;
+            if ((rc = fuse(e, m, {{a + "q", H * dq}, {a + "dkv", Dk}, {a + "g", vd}}, W, L.la_proj, offs))) return rc;
+            L.q_off = offs[0]; L.dkv_off = offs[1]; L.g_off = offs[2];
+            if ((rc = vec_f32(e, m, a + "dkv.norm", d.la_rank, 1, &L.c_norm))) return rc;
+            if ((rc = vec_f32(e, m, a + "sink", H, 1, &L.sink))) return rc;
+            DenseW uk;
+            if ((rc = matrix(e, a + "uk", H * d.head_dim, d.la_rank, uk))) return rc;
+            {
+                const size_t esz = uk.type == T_BF16 ? 2 : 4;
+                void* tp = nullptr;
+                if ((rc = dev_alloc(m, &tp, (size_t)H * d.head_dim * d.la_rank * esz + 64))) return rc;
+                const long n = (long)H * d.head_dim * d.la_rank;
+                transpose_heads_kernel<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>((const unsigned char*)uk.w, (unsigned char*)tp, H, d.head_dim, d.la_rank, (int)esz);
+                CK(cudaGetLastError());
+                L.uk_t.w = tp; L.uk_t.type = uk.type; L.uk_t.N = d.la_rank; L.uk_t.K = d.head_dim;
+            }
+            if ((rc = matrix(e, a + "uv", H * d.la_vdim, d.la_rank, L.uv))) return rc;
+            L.uv.N = d.la_vdim;                       // applied head by head
+            if ((rc = matrix(e, a + "o", W, vd, L.attn_o))) return rc;
+            if ((rc = build_rotary(e, m, L))) return rc;
+            const size_t pool = (size_t)c.kv_num_blocks * c.kv_block_tokens * Dk * cache_esz;
+            if ((rc = dev_alloc(m, &L.la_pool, pool, true))) return rc;
+            e->kv_bytes += (int64_t)pool;
+            max_proj = std::max<size_t>(max_proj, L.la_proj.N);
+            max_buf = std::max<size_t>({max_buf, (size_t)H * Dk, (size_t)vd});
+        } else if (d.mixer == B2_MIX_DELTA_RULE) {
+            const std::string a = p + "mix.";
+            const int H = d.mm_heads, G = d.key_heads, kd = G * d.mm_dim, vd = H * d.mm_vdim;
+            std::vector<int> offs;
+            if ((rc = fuse(e, m, {{a + "q", kd}, {a + "k", kd}, {a + "v", vd}, {a + "b", H}, {a + "a1", d.rank_a}, {a + "g1", d.rank_g}}, W, L.st_proj, offs))) return rc;
+            L.q_off = offs[0]; L.k_off = offs[1]; L.v_off = offs[2]; L.b_off = offs[3]; L.a1_off = offs[4]; L.g1_off = offs[5];
+            L.conv_off = 0; L.conv_C = 2 * kd + vd;
+            if ((rc = concat_f32(e, m, {{a + "q.conv", kd}, {a + "k.conv", kd}, {a + "v.conv", vd}}, d.conv_taps, &L.st_conv_w))) return rc;
+            if ((rc = matrix(e, a + "a2", H * d.mm_dim, d.rank_a, L.a2))) return rc;
+            if ((rc = matrix(e, a + "g2", vd, d.rank_g, L.g2))) return rc;
+            if ((rc = vec_f32(e, m, a + "A_log", H, 1, &L.st_A_log))) return rc;
+            if ((rc = vec_f32(e, m, a + "dt_bias", H * d.mm_dim, 1, &L.st_dt_bias))) return rc;
+            if ((rc = vec_f32(e, m, a + "norm", d.mm_vdim, 1, &L.st_norm))) return rc;
+            if ((rc = matrix(e, a + "o", W, vd, L.st_o))) return rc;
+            if ((rc = dev_alloc(m, (void**)&L.st_conv_state, (size_t)S * std::max(1, d.conv_taps - 1) * L.conv_C * 4, true))) return rc;
+            if ((rc = dev_alloc(m, (void**)&L.st_state, (size_t)S * col_state_floats(H, d.mm_dim, d.mm_vdim) * 4, true))) return rc;
+            max_proj = std::max<size_t>(max_proj, L.st_proj.N);
+            max_buf = std::max<size_t>({max_buf, (size_t)L.conv_C, (size_t)H * d.mm_dim, (size_t)vd});
+        } else if (d.mixer == B2_MIX_SSD) {
+            const std::string a = p + "mix.";
+            const int H = d.mm_heads, inner = H * d.mm_vdim, gn = d.key_heads * d.d_state;
+            if ((rc = matrix(e, a + "in", 2 * inner + 2 * gn + H, W, L.st_proj))) return rc;
+            L.conv_off = inner; L.conv_C = inner + 2 * gn; L.dt_off = 2 * inner + 2 * gn;
+            if ((rc = vec_f32(e, m, a + "conv", d.conv_taps, L.conv_C, &L.st_conv_w))) return rc;
+            if ((rc = vec_f32(e, m, a + "conv.b", L.conv_C, 1, &L.st_conv_b))) return rc;
+            if ((rc = vec_f32(e, m, a + "dt_bias", H, 1, &L.st_dt_bias))) return rc;
+            if ((rc = vec_f32(e, m, a + "A_log", H, 1, &L.st_A_log))) return rc;
+            if ((rc = vec_f32(e, m, a + "D", H, 1, &L.st_D))) return rc;
+            if ((rc = vec_f32(e, m, a + "norm", inner, 1, &L.st_norm))) return rc;
+            if ((rc = matrix(e, a + "o", W, inner, L.st_o))) return rc;
+            if ((rc = dev_alloc(m, (void**)&L.st_conv_state, (size_t)S * std::max(1, d.conv_taps - 1) * L.conv_C * 4, true))) return rc;
+            if ((rc = dev_alloc(m, (void**)&L.st_state, (size_t)S * col_state_floats(H, d.d_state, d.mm_vdim) * 4, true))) return rc;
+            max_proj = std::max<size_t>(max_proj, L.st_proj.N);
+            max_buf = std::max<size_t>({max_buf, (size_t)L.conv_C, (size_t)inner, (size_t)H});
         } else {
             const std::string a = p + "mix.";
             const int qd = d.mm_heads * d.mm_dim, vd = d.mm_heads * d.mm_vdim;
@@ -231,7 +365,17 @@ int layered_finalize(b2_engine* e) {
             max_proj = std::max<size_t>(max_proj, L.mm_proj.N);
             max_buf = std::max<size_t>(max_buf, (size_t)vd);
         }
-        if (d.n_ff > 0) {
+        if (d.n_ff > 0 && d.ff_kind == B2_FF_MOE) {
+            const int slots = d.moe_experts + d.moe_identity;
+            if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
+            if ((rc = matrix(e, p + "mlp.router", slots, W, L.router))) return rc;
+            if ((rc = vec_f32(e, m, p + "mlp.correction", slots, 1, &L.correction))) return rc;
+            if ((rc = stack_experts(e, m, p + "mlp.", d.moe_experts, d.n_ff, W, L.gate_up, L.e_down))) return rc;
+            moe_pairs = std::max<size_t>(moe_pairs, (size_t)Tm * d.moe_top);
+            moe_slots = std::max<size_t>(moe_slots, slots);
+            moe_ff = std::max<size_t>(moe_ff, d.n_ff);
+            moe_experts = std::max<size_t>(moe_experts, d.moe_experts);
+        } else if (d.n_ff > 0) {
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
             if ((rc = matrix(e, p + "mlp.up", d.n_ff, W, L.up))) return rc;
             if ((rc = vec_f32(e, m, p + "mlp.up.b", d.n_ff, 1, &L.up_b))) return rc;
@@ -245,11 +389,24 @@ int layered_finalize(b2_engine* e) {
     for (int i = 0; i < 4; i++) if ((rc = dev_alloc(m, (void**)&m->buf[i], (size_t)Tm * max_buf * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->oL, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->oR, (size_t)Tm * W * 4))) return rc;
+    if ((rc = dev_alloc(m, (void**)&m->hn, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
     if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W}) * 2 + 64))) return rc;
     if (max_attn > 0) {
         m->attn_split_floats = (int)(148 * 2 * (max_attn_d + 2));       // T * H * splits <= 2 * 148 on the split path
         if ((rc = dev_alloc(m, (void**)&m->attn_split, (size_t)m->attn_split_floats * 4))) return rc;
+    }
+    if (moe_pairs > 0) {
+        m->moe_max_tiles = (int)(moe_pairs / 64 + moe_experts + 1);
+        if ((rc = dev_alloc(m, (void**)&m->moe_logits, (size_t)Tm * moe_slots * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_weight, moe_pairs * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_sel, moe_pairs * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_tok, moe_pairs * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_pos, moe_pairs * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_rows, moe_pairs * 4, true))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_tiles, (size_t)(3 * m->moe_max_tiles + 1) * 4, true))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_h, moe_pairs * moe_ff * 4))) return rc;
+        if ((rc = dev_alloc(m, (void**)&m->moe_y, moe_pairs * W * 4))) return rc;
     }
     if ((rc = dev_alloc(m, (void**)&m->rows, (size_t)LOGIT_ROWS * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->logits, (size_t)LOGIT_ROWS * V * 4))) return rc;
@@ -289,6 +446,13 @@ int layered_seq_reset(b2_engine* e, int slot) {
             const size_t cs = (size_t)d.d_inner * std::max(1, d.conv_taps - 1), ss = (size_t)d.d_inner * d.d_state;
             CK(cudaMemsetAsync(L.conv_state + slot * cs, 0, cs * 4, e->stream));
             CK(cudaMemsetAsync(L.ssm_state + slot * ss, 0, ss * 4, e->stream));
+        } else if (d.mixer == B2_MIX_LATENT_ATTN) {
+            // nothing but cache pages, which are overwritten
+        } else if (d.mixer == B2_MIX_DELTA_RULE || d.mixer == B2_MIX_SSD) {
+            const size_t cs = (size_t)std::max(1, d.conv_taps - 1) * L.conv_C;
+            const size_t ss = col_state_floats(d.mm_heads, d.mixer == B2_MIX_SSD ? d.d_state : d.mm_dim, d.mm_vdim);
+            CK(cudaMemsetAsync(L.st_conv_state + slot * cs, 0, cs * 4, e->stream));
+            CK(cudaMemsetAsync(L.st_state + slot * ss, 0, ss * 4, e->stream));
         } else {
             const size_t s1 = (size_t)d.mm_heads * d.mm_dim * d.mm_vdim, s2 = (size_t)d.mm_heads * d.mm_dim;
             CK(cudaMemsetAsync(L.S + slot * s1, 0, s1 * 4, e->stream));
@@ -322,8 +486,32 @@ extern "C" int b2_engine_create_layered(const b2_layered_config* c, const b2_lay
         } else if (d.mixer == B2_MIX_MATRIX_MEMORY) {
             if (d.mm_heads <= 0 || d.mm_dim <= 0 || d.mm_vdim <= 0 || !(d.gate_cap > 0.0)) return b2_fail(B2_ERR_ARG, li + "bad matrix-memory sizes");
             if (d.mm_dim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "matrix-memory key size above 256");
+        } else if (d.mixer == B2_MIX_LATENT_ATTN) {
+            if (d.n_head <= 0 || d.head_dim <= 0 || d.la_rot_dim < 0 || d.la_vdim <= 0 || d.la_rank <= 0) return b2_fail(B2_ERR_ARG, li + "bad latent-attention sizes");
+            if (d.rot_dims < 0 || d.rot_dims > d.la_rot_dim || d.rot_dims % 2) return b2_fail(B2_ERR_ARG, li + "rotary dims must be even and <= the rotated part");
+            if (d.la_rank + d.la_rot_dim > 640) return b2_fail(B2_ERR_UNSUPPORTED, li + "latent + rotated key part above 640");
+        } else if (d.mixer == B2_MIX_DELTA_RULE) {
+            if (d.mm_heads <= 0 || d.key_heads <= 0 || d.mm_heads % d.key_heads || d.mm_dim <= 0 || d.mm_vdim <= 0 || d.rank_a <= 0 || d.rank_g <= 0 ||
+                d.conv_taps <= 0 || d.conv_taps > 64)
+                return b2_fail(B2_ERR_ARG, li + "bad delta-rule sizes");
+            if (d.mm_dim > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "delta-rule key size above 256");
+        } else if (d.mixer == B2_MIX_SSD) {
+            if (d.mm_heads <= 0 || d.key_heads <= 0 || d.mm_heads % d.key_heads || d.d_state <= 0 || d.mm_vdim <= 0 || d.conv_taps <= 0 || d.conv_taps > 64 ||
+                d.norm_groups <= 0 || (d.mm_heads * d.mm_vdim) % d.norm_groups)
+                return b2_fail(B2_ERR_ARG, li + "bad state-space sizes");
+            if (d.d_state > 256) return b2_fail(B2_ERR_UNSUPPORTED, li + "state size above 256");
         } else return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown mixer kind");
+        if (d.n_ff > 0 && d.ff_kind == B2_FF_MOE) {
+            const int slots = d.moe_experts + d.moe_identity;
+            if (d.moe_experts <= 0 || d.moe_identity < 0 || d.moe_top <= 0 || d.moe_top > slots || d.moe_groups <= 0 || slots % d.moe_groups ||
+                d.moe_keep <= 0 || d.moe_keep > d.moe_groups || d.moe_top > d.moe_keep * (slots / d.moe_groups))
+                return b2_fail(B2_ERR_ARG, li + "bad mixture-of-experts sizes");
+            if (slots > 4096) return b2_fail(B2_ERR_UNSUPPORTED, li + "more than 4096 expert slots");
+        } else if (d.ff_kind != B2_FF_RELU2) return b2_fail(B2_ERR_UNSUPPORTED, li + "unknown feed-forward kind");
+        if (c->block_style == B2_BLOCK_PRENORM_RMS ? (d.mixer == B2_MIX_WINDOW_SCAN) : false)
+            return b2_fail(B2_ERR_UNSUPPORTED, li + "the two-branch mixer belongs to post-sum blocks");
     }
+    if (c->block_style != B2_BLOCK_POSTSUM_LN && c->block_style != B2_BLOCK_PRENORM_RMS) return b2_fail(B2_ERR_ARG, "unknown block style");
     b2_engine* e = new b2_engine();
     b2_config& b = e->cfg;
     memset(&b, 0, sizeof(b));
@@ -386,90 +574,302 @@ struct StepProfiler {                 // events around launches of one kind, onl
 }  // namespace
 
 static int dense(b2_engine* e, LayeredModel* m, const DenseW& w, const float* x, int ldx, float* y, int ldy, int T,
-                 const float* bias = nullptr, int epi = EPI_NONE, int kind = 1) {
+                 const float* bias = nullptr, int epi = EPI_NONE, int kind = 1, DenseArgs* more = nullptr) {
     StepProfiler sp(m, e->stream, kind);
-    DenseArgs a = {};
+    DenseArgs a = more ? *more : DenseArgs{};
     a.x = x; a.ldx = ldx; a.w = w.w; a.w_type = w.type; a.bias = bias; a.y = y; a.ldy = ldy; a.T = T; a.N = w.N; a.K = w.K;
-    a.epi = epi; a.exact = m->exact; a.xb = m->xb;
+    a.epi = epi; a.exact = m->exact || (more && more->exact); a.xb = m->xb;
     CK(dense_launch(a, e->stream));
     e->launches++;
     return B2_OK;
+}
+
+// ---- token mixers: each reads the sublayer input `in` [T][W] and leaves its output in m->oL (the two-branch mixer also m->oR)
+static int mix_window_scan(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd;
+    int rc;
+    const int Np = L.in_proj.N, qd = d.n_head * d.head_dim;
+    if ((rc = dense(e, m, L.in_proj, in, W, m->proj, Np, T))) return rc;
+    WindowAttnArgs a = {};
+    a.proj = m->proj; a.ldp = Np; a.q_off = L.q_off; a.k_off = L.k_off; a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm;
+    a.rot.cos = L.rot_cos; a.rot.sin = L.rot_sin; a.rot.rot_dims = d.rot_dims;
+    a.k_pool = L.k_pool; a.v_pool = L.v_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables;
+    a.block_tokens = c.kv_block_tokens; a.H = d.n_head; a.G = d.n_head_kv; a.d = d.head_dim; a.window = d.window;
+    a.keep_first = d.keep_first; a.scale = (float)d.attn_scale; a.eps = c.norm_eps; a.q_rot = m->buf[0]; a.out = m->buf[1];
+    a.split_scratch = m->attn_split; a.split_capacity = m->attn_split_floats;
+    {
+        StepProfiler sp(m, st, 2);
+        CK(window_attn_store_launch(a, r, st));
+        CK(window_attn_launch(a, r, st));
+        e->launches += 2;
+    }
+    if ((rc = dense(e, m, L.attn_o, m->buf[1], qd, m->oL, W, T))) return rc;
+    ScanArgs s = {};
+    s.proj = m->proj; s.ldp = Np; s.x_off = L.x_off; s.z_off = L.z_off; s.conv_w = L.conv_w; s.conv_b = L.conv_b;
+    s.taps = d.conv_taps; s.conv_state = L.conv_state; s.xc = m->buf[0]; s.xproj = m->buf[2];
+    s.ldx = d.dt_rank + 2 * d.d_state; s.R = d.dt_rank; s.N = d.d_state; s.dt_raw = m->buf[3]; s.dt_bias = L.dt_b;
+    s.A_log = L.A_log; s.D = L.Dskip; s.ssm_state = L.ssm_state; s.y = m->buf[1]; s.inner = d.d_inner;
+    {
+        StepProfiler sp(m, st, 3);
+        CK(scan_conv_launch(s, r, st));
+        e->launches++;
+    }
+    if ((rc = dense(e, m, L.scan_x, m->buf[0], d.d_inner, m->buf[2], s.ldx, T))) return rc;
+    if ((rc = dense(e, m, L.scan_dt, m->buf[2], s.ldx, m->buf[3], d.d_inner, T))) return rc;
+    {
+        StepProfiler sp(m, st, 3);
+        CK(scan_recurrence_launch(s, r, st));
+        e->launches += d.d_state <= 32 ? 2 : 1;      // states up to a warp wide: a preparation pass goes first
+    }
+    return dense(e, m, L.scan_o, m->buf[1], d.d_inner, m->oR, W, T);
+}
+
+static int mix_matrix_memory(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    const int T = r.T, W = c.n_embd;
+    int rc;
+    const int Np = L.mm_proj.N, vd = d.mm_heads * d.mm_vdim;
+    if ((rc = dense(e, m, L.mm_proj, in, W, m->proj, Np, T))) return rc;
+    MatrixMemArgs a = {};
+    a.proj = m->proj; a.ldp = Np; a.q_off = L.mq; a.k_off = L.mk; a.v_off = L.mv; a.g_off = L.mg; a.i_off = L.mi; a.f_off = L.mf;
+    a.i_bias = L.i_b; a.f_bias = L.f_b; a.norm_w = L.mm_norm; a.H = d.mm_heads; a.d = d.mm_dim; a.dv = d.mm_vdim;
+    a.cap = (float)d.gate_cap; a.eps = c.norm_eps; a.S = L.S; a.n = L.nvec; a.m = L.mmax; a.o_raw = m->buf[0]; a.out = m->buf[1];
+    {
+        StepProfiler sp(m, e->stream, 4);
+        CK(matrix_mem_launch(a, r, e->stream));
+        e->launches += 3;
+    }
+    return dense(e, m, L.mm_o, m->buf[1], vd, m->oL, W, T);
+}
+
+static int mix_latent_attn(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd, H = d.n_head, dq = d.head_dim + d.la_rot_dim, Dk = d.la_rank + d.la_rot_dim, Np = L.la_proj.N;
+    int rc;
+    if ((rc = dense(e, m, L.la_proj, in, W, m->proj, Np, T))) return rc;
+    LatentAttnArgs a = {};
+    a.proj = m->proj; a.ldp = Np; a.q_off = L.q_off; a.dkv_off = L.dkv_off; a.c_norm_w = L.c_norm;
+    a.rot.cos = L.rot_cos; a.rot.sin = L.rot_sin; a.rot.rot_dims = d.rot_dims;
+    a.pool = L.la_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables; a.block_tokens = c.kv_block_tokens;
+    a.H = H; a.d = d.head_dim; a.dr = d.la_rot_dim; a.rank = d.la_rank; a.window = d.window > 0 ? d.window : c.n_ctx;
+    a.scale = (float)d.attn_scale; a.eps = c.norm_eps; a.sink = L.sink; a.qv = m->buf[0]; a.o_lat = m->buf[1];
+    {
+        StepProfiler sp(m, st, 2);
+        CK(latent_store_launch(a, r, st));
+        e->launches++;
+    }
+    // every head's unrotated query through its transposed key map: the head's query in the latent's coordinates
+    DenseArgs b = {};
+    b.batch = H; b.x_bs = dq; b.w_bs = (long)d.la_rank * d.head_dim; b.y_bs = Dk;
+    if ((rc = dense(e, m, L.uk_t, m->proj + L.q_off, Np, m->buf[0], H * Dk, T, nullptr, EPI_NONE, 1, &b))) return rc;
+    {
+        StepProfiler sp(m, st, 2);
+        CK(latent_attn_launch(a, r, st));
+        e->launches++;
+    }
+    // values of the weighted latent sums, head by head, times the sigmoid output gate
+    DenseArgs v = {};
+    v.batch = H; v.x_bs = d.la_rank; v.w_bs = (long)d.la_vdim * d.la_rank; v.y_bs = d.la_vdim;
+    v.aux = m->proj + L.g_off; v.ldaux = Np; v.aux_bs = d.la_vdim;
+    if ((rc = dense(e, m, L.uv, m->buf[1], H * d.la_rank, m->buf[2], H * d.la_vdim, T, nullptr, EPI_MUL_SIGMOID, 1, &v))) return rc;
+    return dense(e, m, L.attn_o, m->buf[2], H * d.la_vdim, m->oL, W, T);
+}
+
+static int mix_delta_rule(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd, H = d.mm_heads, G = d.key_heads, kd = G * d.mm_dim, vd = H * d.mm_vdim, Np = L.st_proj.N;
+    int rc;
+    if ((rc = dense(e, m, L.st_proj, in, W, m->proj, Np, T))) return rc;
+    ConvArgs cv = {};
+    cv.in = m->proj + L.conv_off; cv.ld_in = Np; cv.C = L.conv_C; cv.taps = d.conv_taps; cv.w = L.st_conv_w; cv.bias = nullptr;
+    cv.state = L.st_conv_state; cv.out = m->buf[0]; cv.ld_out = L.conv_C;
+    {
+        StepProfiler sp(m, st, 3);
+        CK(causal_conv_launch(cv, r, st));
+        CK(causal_conv_advance_launch(cv, r, st));
+        e->launches += d.conv_taps > 1 ? 2 : 1;
+    }
+    if ((rc = dense(e, m, L.a2, m->proj + L.a1_off, Np, m->buf[1], H * d.mm_dim, T))) return rc;
+    if ((rc = dense(e, m, L.g2, m->proj + L.g1_off, Np, m->buf[2], vd, T))) return rc;
+    DeltaPrepArgs pa = {};
+    pa.q = m->buf[0]; pa.k = m->buf[0] + kd; pa.ld_qk = L.conv_C; pa.G = G; pa.d = d.mm_dim;
+    pa.a = m->buf[1]; pa.ld_a = H * d.mm_dim; pa.A_log = L.st_A_log; pa.dt_bias = L.st_dt_bias; pa.H = H;
+    pa.beta = m->proj + L.b_off; pa.ld_b = Np; pa.unit_eps = 1e-6f;
+    ColStateArgs cs = {};
+    cs.wk = m->buf[0] + kd; cs.ld_wk = L.conv_C; cs.rk = m->buf[0]; cs.ld_rk = L.conv_C;
+    cs.row_decay = m->buf[1]; cs.ld_rd = H * d.mm_dim; cs.val = m->buf[0] + 2 * kd; cs.ld_v = L.conv_C;
+    cs.val_scale = m->proj + L.b_off; cs.ld_vs = Np; cs.H = H; cs.G = G; cs.R = d.mm_dim; cs.P = d.mm_vdim; cs.delta = 1;
+    cs.state = L.st_state; cs.y = m->buf[3]; cs.ld_y = vd;
+    GroupNormArgs gn = {};
+    gn.x = m->buf[3]; gn.ld_x = vd; gn.gate = m->buf[2]; gn.ld_g = vd; gn.w = L.st_norm; gn.w_gstride = 0; gn.groups = H; gn.n = d.mm_vdim;
+    gn.eps = c.norm_eps; gn.gate_first = 0; gn.y = m->buf[3]; gn.ld_y = vd;
+    {
+        StepProfiler sp(m, st, 4);
+        CK(delta_prepare_launch(pa, T, st));
+        CK(col_state_launch(cs, r, st));
+        CK(group_norm_gate_launch(gn, T, st));
+        e->launches += 3;
+    }
+    return dense(e, m, L.st_o, m->buf[3], vd, m->oL, W, T);
+}
+
+static int mix_ssd(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layered_config& c = m->c;
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = c.n_embd, H = d.mm_heads, G = d.key_heads, N = d.d_state, inner = H * d.mm_vdim, Np = L.st_proj.N;
+    int rc;
+    if ((rc = dense(e, m, L.st_proj, in, W, m->proj, Np, T))) return rc;
+    ConvArgs cv = {};
+    cv.in = m->proj + L.conv_off; cv.ld_in = Np; cv.C = L.conv_C; cv.taps = d.conv_taps; cv.w = L.st_conv_w; cv.bias = L.st_conv_b;
+    cv.state = L.st_conv_state; cv.out = m->buf[0]; cv.ld_out = L.conv_C;
+    ColStateArgs cs = {};
+    cs.wk = m->buf[0] + inner; cs.ld_wk = L.conv_C; cs.rk = m->buf[0] + inner + G * N; cs.ld_rk = L.conv_C;
+    cs.head_decay = m->buf[1]; cs.ld_hd = H; cs.val = m->buf[0]; cs.ld_v = L.conv_C;
+    cs.val_scale = m->proj + L.dt_off; cs.ld_vs = Np; cs.skip = L.st_D; cs.H = H; cs.G = G; cs.R = N; cs.P = d.mm_vdim; cs.delta = 0;
+    cs.state = L.st_state; cs.y = m->buf[2]; cs.ld_y = inner;
+    GroupNormArgs gn = {};
+    gn.x = m->buf[2]; gn.ld_x = inner; gn.gate = m->proj; gn.ld_g = Np; gn.w = L.st_norm; gn.w_gstride = inner / d.norm_groups;
+    gn.groups = d.norm_groups; gn.n = inner / d.norm_groups; gn.eps = c.norm_eps; gn.gate_first = 1; gn.y = m->buf[2]; gn.ld_y = inner;
+    {
+        StepProfiler sp(m, st, 3);
+        CK(causal_conv_launch(cv, r, st));
+        CK(causal_conv_advance_launch(cv, r, st));
+        CK(ssd_prepare_launch(m->proj + L.dt_off, Np, L.st_dt_bias, L.st_A_log, H, m->buf[1], T, st));
+        CK(col_state_launch(cs, r, st));
+        CK(group_norm_gate_launch(gn, T, st));
+        e->launches += d.conv_taps > 1 ? 5 : 4;
+    }
+    return dense(e, m, L.st_o, m->buf[2], inner, m->oL, W, T);
+}
+
+// ---- feed-forward blocks: input `in` [T][W], output in m->oL
+static int ff_relu2(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const int T = r.T, W = m->c.n_embd;
+    int rc;
+    if ((rc = dense(e, m, L.up, in, W, m->ff, L.d.n_ff, T, L.up_b, EPI_BIAS_RELU2))) return rc;
+    return dense(e, m, L.down, m->ff, L.d.n_ff, m->oL, W, T, L.down_b, EPI_BIAS);
+}
+
+static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    const b2_layer_desc& d = L.d;
+    cudaStream_t st = e->stream;
+    const int T = r.T, W = m->c.n_embd, slots = d.moe_experts + d.moe_identity, pairs = T * d.moe_top, ff = d.n_ff;
+    int rc;
+    DenseArgs ex = {};
+    ex.exact = true;                               // router scores are 32-bit products
+    if ((rc = dense(e, m, L.router, in, W, m->moe_logits, slots, T, nullptr, EPI_NONE, 7, &ex))) return rc;
+    MoeRouteArgs ra = {};
+    ra.logits = m->moe_logits; ra.ld = slots; ra.correction = L.correction; ra.n_slots = slots; ra.n_experts = d.moe_experts;
+    ra.top = d.moe_top; ra.n_groups = d.moe_groups; ra.keep_groups = d.moe_keep; ra.scale = (float)d.moe_scale;
+    ra.sel = m->moe_sel; ra.weight = m->moe_weight; ra.pair_token = m->moe_tok;
+    DenseGroups g = {};
+    g.n_groups = d.moe_experts;
+    const bool tiled = T > 8;
+    {
+        StepProfiler sp(m, st, 7);
+        CK(moe_route_launch(ra, T, st));
+        e->launches++;
+        if (tiled) {
+            MoeSortArgs sa = {};
+            sa.sel = m->moe_sel; sa.n_pairs = pairs; sa.top = d.moe_top; sa.n_experts = d.moe_experts; sa.pos = m->moe_pos; sa.x_rows = m->moe_rows;
+            sa.n_tiles = m->moe_tiles; sa.tile_group = m->moe_tiles + 1; sa.tile_row0 = sa.tile_group + m->moe_max_tiles;
+            sa.tile_rows = sa.tile_row0 + m->moe_max_tiles; sa.max_tiles = m->moe_max_tiles;
+            CK(moe_sort_launch(sa, st));
+            e->launches++;
+            g.tile_group = sa.tile_group; g.tile_row0 = sa.tile_row0; g.tile_rows = sa.tile_rows; g.n_tiles = sa.n_tiles;
+            g.max_tiles = std::min(m->moe_max_tiles, pairs / 64 + d.moe_experts + 1);
+        } else g.group = m->moe_sel;
+    }
+    DenseArgs up = {};
+    g.x_rows = tiled ? m->moe_rows : m->moe_tok; g.w_stride = (long)2 * ff * W;
+    up.groups = &g;
+    if ((rc = dense(e, m, L.gate_up, in, W, m->moe_h, ff, pairs, nullptr, EPI_GLU_SILU, 1, &up))) return rc;
+    DenseGroups g2 = g;
+    g2.x_rows = nullptr; g2.w_stride = (long)W * ff;
+    DenseArgs dn = {};
+    dn.groups = &g2;
+    if ((rc = dense(e, m, L.e_down, m->moe_h, ff, m->moe_y, W, pairs, nullptr, EPI_NONE, 1, &dn))) return rc;
+    StepProfiler sp(m, st, 7);
+    CK(moe_combine_launch(m->moe_sel, m->moe_weight, tiled ? m->moe_pos : nullptr, m->moe_y, in, d.moe_experts, d.moe_top, W, T, m->oL, st));
+    e->launches++;
+    return B2_OK;
+}
+
+static int run_mixer(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    switch (L.d.mixer) {
+        case B2_MIX_WINDOW_SCAN: return mix_window_scan(e, m, L, r, in);
+        case B2_MIX_MATRIX_MEMORY: return mix_matrix_memory(e, m, L, r, in);
+        case B2_MIX_LATENT_ATTN: return mix_latent_attn(e, m, L, r, in);
+        case B2_MIX_DELTA_RULE: return mix_delta_rule(e, m, L, r, in);
+        case B2_MIX_SSD: return mix_ssd(e, m, L, r, in);
+    }
+    return b2_fail(B2_ERR_UNSUPPORTED, "unknown mixer kind");
+}
+static int run_ff(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+    return L.d.ff_kind == B2_FF_MOE ? ff_moe(e, m, L, r, in) : ff_relu2(e, m, L, r, in);
 }
 
 static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
     const b2_layered_config& c = m->c;
     cudaStream_t st = e->stream;
     const int T = r.T, W = c.n_embd;
+    const bool prenorm = c.block_style == B2_BLOCK_PRENORM_RMS;
     int rc;
     {
         StepProfiler sp(m, st, 0);
         CK(embed_ragged_launch(m->embed.w, m->embed.type, W, r.tok_id, T, m->x, st));
         e->launches++;
+        if (prenorm) {
+            CK(resid_rms_norm_launch(m->x, nullptr, 0.f, m->embed_norm, 1.f, 1.f, c.norm_eps, W, T, m->x, st));
+            e->launches++;
+        }
     }
+    // pre-norm blocks: a branch output waits in m->oL until the next norm (or the end of the layer) adds it to the stream
+    const float* pending = nullptr;
+    auto join = [&](const float* norm_w, float* y) -> int {
+        StepProfiler sp(m, st, 5);
+        CK(resid_rms_norm_launch(m->x, pending, c.residual_scale, norm_w, 1.f, 1.f, c.norm_eps, W, T, y, st));
+        e->launches++;
+        pending = nullptr;
+        return B2_OK;
+    };
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
-        if (d.mixer == B2_MIX_WINDOW_SCAN) {
-            const int Np = L.in_proj.N, qd = d.n_head * d.head_dim;
-            if ((rc = dense(e, m, L.in_proj, m->x, W, m->proj, Np, T))) return rc;
-            WindowAttnArgs a = {};
-            a.proj = m->proj; a.ldp = Np; a.q_off = L.q_off; a.k_off = L.k_off; a.q_norm_w = L.q_norm; a.k_norm_w = L.k_norm;
-            a.rot.cos = L.rot_cos; a.rot.sin = L.rot_sin; a.rot.rot_dims = d.rot_dims;
-            a.k_pool = L.k_pool; a.v_pool = L.v_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables;
-            a.block_tokens = c.kv_block_tokens; a.H = d.n_head; a.G = d.n_head_kv; a.d = d.head_dim; a.window = d.window;
-            a.keep_first = d.keep_first; a.scale = (float)d.attn_scale; a.eps = c.norm_eps; a.q_rot = m->buf[0]; a.out = m->buf[1];
-            a.split_scratch = m->attn_split; a.split_capacity = m->attn_split_floats;
-            {
-                StepProfiler sp(m, st, 2);
-                CK(window_attn_store_launch(a, r, st));
-                CK(window_attn_launch(a, r, st));
-                e->launches += 2;
+        if (prenorm) {
+            if ((rc = join(L.norm1, m->hn))) return rc;
+            if ((rc = run_mixer(e, m, L, r, m->hn))) return rc;
+            pending = m->oL;
+            if (d.n_ff > 0) {
+                if ((rc = join(L.norm2, m->hn))) return rc;
+                if ((rc = run_ff(e, m, L, r, m->hn))) return rc;
+                pending = m->oL;
             }
-            if ((rc = dense(e, m, L.attn_o, m->buf[1], qd, m->oL, W, T))) return rc;
-            ScanArgs s = {};
-            s.proj = m->proj; s.ldp = Np; s.x_off = L.x_off; s.z_off = L.z_off; s.conv_w = L.conv_w; s.conv_b = L.conv_b;
-            s.taps = d.conv_taps; s.conv_state = L.conv_state; s.xc = m->buf[0]; s.xproj = m->buf[2];
-            s.ldx = d.dt_rank + 2 * d.d_state; s.R = d.dt_rank; s.N = d.d_state; s.dt_raw = m->buf[3]; s.dt_bias = L.dt_b;
-            s.A_log = L.A_log; s.D = L.Dskip; s.ssm_state = L.ssm_state; s.y = m->buf[1]; s.inner = d.d_inner;
+            if (m->trace || li == c.n_layer - 1) { if ((rc = join(nullptr, nullptr))) return rc; }
+        } else {
+            if ((rc = run_mixer(e, m, L, r, m->x))) return rc;
             {
-                StepProfiler sp(m, st, 3);
-                CK(scan_conv_launch(s, r, st));
+                const bool two = d.mixer == B2_MIX_WINDOW_SCAN;
+                StepProfiler sp(m, st, 5);
+                CK(postsum_norm_launch(m->x, m->oL, two ? L.left_w : nullptr, two ? m->oR : nullptr, two ? L.right_w : nullptr, L.norm1,
+                                       c.residual_scale, c.norm_eps, W, T, st));
                 e->launches++;
             }
-            if ((rc = dense(e, m, L.scan_x, m->buf[0], d.d_inner, m->buf[2], s.ldx, T))) return rc;
-            if ((rc = dense(e, m, L.scan_dt, m->buf[2], s.ldx, m->buf[3], d.d_inner, T))) return rc;
-            {
-                StepProfiler sp(m, st, 3);
-                CK(scan_recurrence_launch(s, r, st));
-                e->launches += d.d_state <= 32 ? 2 : 1;      // states up to a warp wide: a preparation pass goes first
+            if (d.n_ff > 0) {
+                if ((rc = run_ff(e, m, L, r, m->x))) return rc;
+                StepProfiler sp(m, st, 5);
+                CK(postsum_norm_launch(m->x, m->oL, nullptr, nullptr, nullptr, L.norm2, c.residual_scale, c.norm_eps, W, T, st));
+                e->launches++;
             }
-            if ((rc = dense(e, m, L.scan_o, m->buf[1], d.d_inner, m->oR, W, T))) return rc;
-            StepProfiler sp(m, st, 5);
-            CK(postsum_norm_launch(m->x, m->oL, L.left_w, m->oR, L.right_w, L.norm1, c.residual_scale, c.norm_eps, W, T, st));
-            e->launches++;
-        } else {
-            const int Np = L.mm_proj.N, vd = d.mm_heads * d.mm_vdim;
-            if ((rc = dense(e, m, L.mm_proj, m->x, W, m->proj, Np, T))) return rc;
-            MatrixMemArgs a = {};
-            a.proj = m->proj; a.ldp = Np; a.q_off = L.mq; a.k_off = L.mk; a.v_off = L.mv; a.g_off = L.mg; a.i_off = L.mi; a.f_off = L.mf;
-            a.i_bias = L.i_b; a.f_bias = L.f_b; a.norm_w = L.mm_norm; a.H = d.mm_heads; a.d = d.mm_dim; a.dv = d.mm_vdim;
-            a.cap = (float)d.gate_cap; a.eps = c.norm_eps; a.S = L.S; a.n = L.nvec; a.m = L.mmax; a.o_raw = m->buf[0]; a.out = m->buf[1];
-            {
-                StepProfiler sp(m, st, 4);
-                CK(matrix_mem_launch(a, r, st));
-                e->launches += 3;
-            }
-            if ((rc = dense(e, m, L.mm_o, m->buf[1], vd, m->oL, W, T))) return rc;
-            StepProfiler sp(m, st, 5);
-            CK(postsum_norm_launch(m->x, m->oL, nullptr, nullptr, nullptr, L.norm1, c.residual_scale, c.norm_eps, W, T, st));
-            e->launches++;
-        }
-        if (d.n_ff > 0) {
-            if ((rc = dense(e, m, L.up, m->x, W, m->ff, d.n_ff, T, L.up_b, EPI_BIAS_RELU2))) return rc;
-            if ((rc = dense(e, m, L.down, m->ff, d.n_ff, m->oL, W, T, L.down_b, EPI_BIAS))) return rc;
-            StepProfiler sp(m, st, 5);
-            CK(postsum_norm_launch(m->x, m->oL, nullptr, nullptr, nullptr, L.norm2, c.residual_scale, c.norm_eps, W, T, st));
-            e->launches++;
         }
         if (m->trace)
             CK(cudaMemcpyAsync(m->trace + ((size_t)li * c.max_step_tokens) * W, m->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
@@ -546,10 +946,13 @@ extern "C" int b2_step(b2_engine* e, int n_entries, const int32_t* slots, const 
         {
             StepProfiler sp(m, st, 5);
             CK(gather_rows_launch(m->x, W, d_rows + r0, nr, m->rows, st));
-            CK(layer_norm_launch(m->rows, m->final_norm, c.norm_eps, W, nr, m->rows, st));
+            if (c.block_style == B2_BLOCK_PRENORM_RMS) CK(resid_rms_norm_launch(m->rows, nullptr, 0.f, m->final_norm, 1.f, 1.f, c.norm_eps, W, nr, m->rows, st));
+            else CK(layer_norm_launch(m->rows, m->final_norm, c.norm_eps, W, nr, m->rows, st));
             e->launches += 2;
         }
-        int rc2 = dense(e, m, m->head, m->rows, W, m->logits, V, nr, nullptr, EPI_NONE, 6);
+        DenseArgs hs = {};
+        hs.scale = c.logit_scale != 0.f ? c.logit_scale : 1.f;
+        int rc2 = dense(e, m, m->head, m->rows, W, m->logits, V, nr, nullptr, EPI_NONE, 6, &hs);
         if (rc2) return rc2;
         const int n_w = std::max(0, std::min(n_want - r0, nr));
         if (n_w > 0) CK(cudaMemcpyAsync(m->logits_host, m->logits, (size_t)n_w * V * 4, cudaMemcpyDeviceToHost, st));

@@ -30,7 +30,24 @@ struct RaggedDev {             // device pointers, valid for one step
 // ---------------------------------------------------------------- dense products (dense.cu)
 // Y[t][n] = epi(sum_k X[t][k] * W[n][k] (+ bias[n])), X f32 [T][ldx], W [N][K] (bf16 or f32), Y f32 [T][ldy].
 // Each output element is one fixed-order sum over k: a row's result does not depend on what else is in the batch.
-enum DenseEpi { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU2 = 2 };
+// EPI_GLU_SILU: weight rows come in pairs (2i = gate, 2i + 1 = up); output column i = silu(gate) * up, N counts weight rows.
+// EPI_MUL_SIGMOID: the product times sigmoid(aux[t][n]).
+enum DenseEpi { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU2 = 2, EPI_GLU_SILU = 3, EPI_MUL_SIGMOID = 4 };
+// Grouped products (mixture of experts): the rows of a step's (token, choice) pairs, each against the matrix of its group.
+//   tiles == nullptr: row p of the product is pair p itself, blockIdx.y walks the pairs one by one (few-token steps);
+//   else: pairs sorted by group, tile i = rows [tile_row0[i], + tile_rows[i]) of group tile_group[i]; *n_tiles of them.
+// The input row of pair row p is x_rows ? x_rows[p] : p; pairs whose group is >= n_groups (or < 0) are skipped.
+struct DenseGroups {
+    const int* group = nullptr;        // untiled: [rows] group of each row
+    const int* x_rows = nullptr;       // [rows] input row of each product row, or null
+    const int* tile_group = nullptr;   // tiled: per tile
+    const int* tile_row0 = nullptr;
+    const int* tile_rows = nullptr;
+    const int* n_tiles = nullptr;      // device scalar
+    int n_groups = 0;
+    long w_stride = 0;                 // elements between the matrices of two groups
+    int max_tiles = 0;                 // grid size of a tiled launch
+};
 struct DenseArgs {
     const float* x; int ldx;
     const void* w; int w_type;      // T_BF16 or T_F32 (quant_blocks.cuh ids)
@@ -40,6 +57,11 @@ struct DenseArgs {
     int epi;
     bool exact;                     // true: 32-bit multiply-adds (no tensor cores, inputs not rounded)
     __nv_bfloat16* xb;              // scratch [T][K] for X rounded to bf16 (large tensor-core steps); null: not available
+    float scale = 1.f;              // the product (after the epilogue) times this
+    const float* aux = nullptr; int ldaux = 0;      // EPI_MUL_SIGMOID
+    // batch > 1: `batch` independent products, operand b at x + b * x_bs, w + b * w_bs (elements), y + b * y_bs, aux + b * aux_bs
+    int batch = 1; long x_bs = 0, w_bs = 0, y_bs = 0, aux_bs = 0;
+    const DenseGroups* groups = nullptr;            // grouped product (T = number of pair rows)
 };
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s);
 
@@ -53,6 +75,10 @@ cudaError_t gather_rows_launch(const float* x, int W, const int* rows, int n, fl
 //   y = (rms(a) * wa + rms(b) * wb) / 2   (two branches, each RMS-normed over the width first)
 cudaError_t postsum_norm_launch(float* x, const float* a, const float* wa, const float* b, const float* wb, const float* w,
                                 float alpha, float eps, int W, int T, cudaStream_t s);
+// Pre-norm blocks: if (add) x[t] += mult * add[t]; if (y) y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * (w_offset + w) * out_scale.
+// y may be x itself.
+cudaError_t resid_rms_norm_launch(float* x, const float* add, float mult, const float* w, float w_offset, float out_scale,
+                                  float eps, int W, int T, float* y, cudaStream_t s);
 // plain layer norm without bias: y[t] = LN(x[t]) * w
 cudaError_t layer_norm_launch(const float* x, const float* w, float eps, int W, int T, float* y, cudaStream_t s);
 
@@ -106,6 +132,104 @@ struct MatrixMemArgs {         // mLSTM
     float* out;                // [T][H*dv]
 };
 cudaError_t matrix_mem_launch(const MatrixMemArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// ---------------------------------------------------------------- short causal convolution (state_mixers.cu)
+// out[t][c] = silu(bias[c] + sum_j w[c][j] * in[t - (taps-1) + j][c]) over C neighbouring columns of `in`; inputs before the
+// step come from the slot's state (the last taps-1 inputs, [slot][taps-1][C]), zeros before the sequence.
+struct ConvArgs {
+    const float* in; int ld_in;
+    int C, taps;
+    const float* w; const float* bias;      // [C][taps]; [C] or null
+    float* state;
+    float* out; int ld_out;
+};
+cudaError_t causal_conv_launch(const ConvArgs& a, const RaggedDev& r, cudaStream_t s);
+// the state moves on to the last taps-1 inputs of every segment (after causal_conv_launch has read the old one)
+cudaError_t causal_conv_advance_launch(const ConvArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// ---------------------------------------------------------------- matrix-state recurrences (state_mixers.cu)
+// Per head a memory S [R rows][P columns], 32-bit, one per sequence slot. For every token of a segment, in order:
+//   S[r][:] *= row_decay[r] * head_decay          (either may be absent)
+//   u = val_scale * (val - (delta ? S^T wk : 0))  (delta rule: write only what the memory does not return yet)
+//   S += wk u^T ;  y = S^T rk + skip * val        (the read-out sees the current token's write)
+// Covers the gated delta rule (row decays, delta = 1) and the Mamba-2 state-space recurrence (head decay, skip).
+struct ColStateArgs {
+    const float* wk; int ld_wk;            // [T][G * R] write keys
+    const float* rk; int ld_rk;            // [T][G * R] read keys
+    const float* row_decay; int ld_rd;     // [T][H * R] or null
+    const float* head_decay; int ld_hd;    // [T][H] or null
+    const float* val; int ld_v;            // [T][H * P]
+    const float* val_scale; int ld_vs;     // [T][H]
+    const float* skip;                     // [H] or null
+    int H, G, R, P, delta;
+    float* state;                          // [slot][H][P][Rp], Rp = R rounded up to 4 (column-major, pads stay zero)
+    float* y; int ld_y;                    // [T][H * P]
+};
+inline size_t col_state_floats(int H, int R, int P) { return (size_t)H * P * ((R + 3) / 4 * 4); }
+cudaError_t col_state_launch(const ColStateArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// Delta-rule inputs, in place: q and k [T][G*d] to unit length per head (q also times d^-1/2), the decay columns
+// a [T][H*d] <- exp(-exp(A_log[h]) * softplus(a + dt_bias)), beta [T][H] <- sigmoid(beta).
+struct DeltaPrepArgs {
+    float* q; float* k; int ld_qk; int G, d;
+    float* a; int ld_a; const float* A_log; const float* dt_bias; int H;
+    float* beta; int ld_b;
+    float unit_eps;
+};
+cudaError_t delta_prepare_launch(const DeltaPrepArgs& a, int T, cudaStream_t s);
+// Mamba-2 step sizes, in place: dt [T][H] <- softplus(dt + dt_bias[h]); decay [T][H] = exp(-exp(A_log[h]) * dt)
+cudaError_t ssd_prepare_launch(float* dt, int ld_dt, const float* dt_bias, const float* A_log, int H, float* decay, int T, cudaStream_t s);
+
+// RMS norm over groups of n neighbouring columns with a gate. gate_first = 0: y = x / rms(x) * w * sigmoid(gate);
+// gate_first = 1: v = x * silu(gate), y = v / rms(v) * w. w index: group * w_gstride + i.
+struct GroupNormArgs {
+    const float* x; int ld_x; const float* gate; int ld_g; const float* w; int w_gstride;
+    int groups, n; float eps; int gate_first;
+    float* y; int ld_y;
+};
+cudaError_t group_norm_gate_launch(const GroupNormArgs& a, int T, cudaStream_t s);
+
+// ---------------------------------------------------------------- latent attention (latent_attn.cu)
+// Every token caches one row [c (rank) | rotated shared key part (dr)]; all heads read the same rows. With the per-head
+// key expansion folded into the query (qv[t][h] = [W_uk,h^T q_h | rotated q part]) a head's score is one dot product with
+// the cached row, and the attention output is a weighted sum of the c parts, expanded to values afterwards.
+// Sliding window; the softmax denominator also holds exp(sink[h]).
+struct LatentAttnArgs {
+    const float* proj; int ldp; int q_off, dkv_off;   // q [H][d + dr], dkv [rank + dr]
+    const float* c_norm_w;                            // [rank]
+    RotaryTable rot;                                  // pairs (i, i + rot_dims / 2)
+    void* pool; int cache_f32;                        // pages [page][block_tokens][rank + dr]
+    int* const* block_tables; int block_tokens;
+    int H, d, dr, rank, window;
+    float scale, eps;
+    const float* sink;                                // [H]
+    float* qv;                                        // [T][H][rank + dr]; the first `rank` of each head are filled by the caller
+    float* o_lat;                                     // [T][H][rank]
+};
+// norm of c, rotation of the shared key part, both into the pages; rotated query parts into qv
+cudaError_t latent_store_launch(const LatentAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+cudaError_t latent_attn_launch(const LatentAttnArgs& a, const RaggedDev& r, cudaStream_t s);
+
+// ---------------------------------------------------------------- mixture of experts (moe.cu)
+struct MoeRouteArgs {
+    const float* logits; int ld;           // [T][n_slots] router outputs (32-bit products)
+    const float* correction;               // [n_slots]
+    int n_slots, n_experts, top, n_groups, keep_groups;
+    float scale;
+    int* sel; float* weight;               // [T][top]
+    int* pair_token;                       // [T][top]: t (the input row of each pair)
+};
+cudaError_t moe_route_launch(const MoeRouteArgs& a, int T, cudaStream_t s);
+// pairs sorted by expert into 64-row tiles: pos[p] = row of pair p in the sorted order (-1: identity slot), x_rows[row] =
+// token of that row, and the tile table; all in device memory (meta: [0] = number of tiles)
+struct MoeSortArgs {
+    const int* sel; int n_pairs, top, n_experts;
+    int* pos; int* x_rows; int* tile_group; int* tile_row0; int* tile_rows; int* n_tiles; int max_tiles;
+};
+cudaError_t moe_sort_launch(const MoeSortArgs& a, cudaStream_t s);
+// out[t] = sum over the token's choices, in choice order, of weight * (expert output row | h[t] for identity slots)
+cudaError_t moe_combine_launch(const int* sel, const float* weight, const int* pos, const float* rows, const float* h, int n_experts,
+                               int top, int W, int T, float* out, cudaStream_t s);
 
 // ---------------------------------------------------------------- graph (layered.cu)
 struct LayeredModel;

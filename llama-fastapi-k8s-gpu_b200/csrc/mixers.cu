@@ -104,6 +104,31 @@ cudaError_t postsum_norm_launch(float* x, const float* a, const float* wa, const
     return launch_chain(postsum_norm_kernel, dim3(T), dim3(256), (size_t)W * 4, s, x, a, wa, b, wb, w, alpha, eps, W);
 }
 
+// pre-norm blocks: the pending branch output joins the 32-bit residual stream, and the next sublayer's input is made in the same pass
+__global__ void __launch_bounds__(256) resid_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ add, float mult,
+                                                             const float* __restrict__ w, float w_offset, float out_scale, float eps, int W,
+                                                             float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = x[base + i];
+        if (add) { v = fmaf(mult, add[base + i], v); x[base + i] = v; }
+        row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!y) return;
+    const float rinv = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[base + i] = row[i] * rinv * (w_offset + w[i]) * out_scale;
+}
+cudaError_t resid_rms_norm_launch(float* x, const float* add, float mult, const float* w, float w_offset, float out_scale,
+                                  float eps, int W, int T, float* y, cudaStream_t s) {
+    return launch_chain(resid_rms_norm_kernel, dim3(T), dim3(256), (size_t)W * 4, s, x, add, mult, w, w_offset, out_scale, eps, W, y);
+}
+
 __global__ void __launch_bounds__(256) layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int W,
                                                          float* __restrict__ y) {
     griddep_launch();

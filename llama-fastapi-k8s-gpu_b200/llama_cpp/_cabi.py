@@ -15,7 +15,9 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libb200gguf.so")
 
 B2_FLAG_NO_GRAPH, B2_FLAG_NO_PDL, B2_FLAG_ACT8, B2_FLAG_F32 = 1, 2, 4, 8
 B2_TYPE_F32, B2_TYPE_F16, B2_TYPE_I32, B2_TYPE_BF16 = 0, 1, 26, 30
-B2_MIX_WINDOW_SCAN, B2_MIX_MATRIX_MEMORY = 1, 2
+B2_MIX_WINDOW_SCAN, B2_MIX_MATRIX_MEMORY, B2_MIX_LATENT_ATTN, B2_MIX_DELTA_RULE, B2_MIX_SSD = 1, 2, 3, 4, 5
+B2_FF_RELU2, B2_FF_MOE = 0, 1
+B2_BLOCK_POSTSUM_LN, B2_BLOCK_PRENORM_RMS = 0, 1
 B2_STEP_MAX_ENTRIES = 64
 
 
@@ -31,12 +33,16 @@ class B2LayerDesc(ctypes.Structure):
                                        "rope_orig_ctx", "pad0_")] + [
         (n, c_double) for n in ("attn_scale", "rope_base", "rope_factor", "rope_fast", "rope_slow")] + [
         (n, c_int32) for n in ("conv_taps", "dt_rank", "d_inner", "d_state", "mm_heads", "mm_dim", "mm_vdim", "pad_")] + [
-        ("gate_cap", c_double)]
+        ("gate_cap", c_double)] + [
+        (n, c_int32) for n in ("la_rot_dim", "la_vdim", "la_rank", "ff_kind", "key_heads", "rank_a", "rank_g", "norm_groups",
+                               "moe_experts", "moe_identity", "moe_top", "moe_groups", "moe_keep", "pad1_")] + [
+        ("moe_scale", c_double)]
 
 
 class B2LayeredConfig(ctypes.Structure):
     _fields_ = [(n, c_int32) for n in ("n_layer", "n_embd", "n_vocab")] + [("norm_eps", c_float), ("residual_scale", c_float)] + [
-        (n, c_int32) for n in ("n_ctx", "max_seqs", "kv_block_tokens", "kv_num_blocks", "max_step_tokens", "device", "flags")]
+        (n, c_int32) for n in ("n_ctx", "max_seqs", "kv_block_tokens", "kv_num_blocks", "max_step_tokens", "device", "flags",
+                               "block_style")] + [("logit_scale", c_float)]
 
 
 class B2Sampling(ctypes.Structure):

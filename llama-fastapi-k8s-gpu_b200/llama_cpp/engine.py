@@ -290,7 +290,8 @@ class LayeredEngine(EngineBase):
         if dtype == "float32":
             flags |= _cabi.B2_FLAG_F32
         cfg = _cabi.B2LayeredConfig(dims.n_layer, dims.n_embd, dims.n_vocab, dims.norm_eps, dims.residual_scale, self.n_ctx,
-                                    self.max_seqs, self.block_tokens, self.pages.num_blocks, self.max_step_tokens, self.device, flags)
+                                    self.max_seqs, self.block_tokens, self.pages.num_blocks, self.max_step_tokens, self.device, flags,
+                                    getattr(dims, "block_style", 0), getattr(dims, "logit_scale", 1.0))
         descs = (_cabi.B2LayerDesc * dims.n_layer)(*dims.layers)
         h = ctypes.c_void_p()
         check(self.lib.b2_engine_create_layered(ctypes.byref(cfg), descs, ctypes.byref(h)), "b2_engine_create_layered")
@@ -382,7 +383,7 @@ class LayeredEngine(EngineBase):
         ms = (ctypes.c_float * 8)()
         nl = (ctypes.c_int32 * 8)()
         check(self.lib.b2_step_profile_read(self._h, ms, nl), "b2_step_profile_read")
-        kinds = ["embed", "dense", "attention", "scan", "matrix_memory", "norms", "head"]
+        kinds = ["embed", "dense", "attention", "scan", "matrix_memory", "norms", "head", "routing"]
         return {k: dict(ms=ms[i], launches=nl[i]) for i, k in enumerate(kinds)}
 
     def mode(self) -> dict:

@@ -28,6 +28,8 @@ class LayeredDims:
     residual_scale: float
     layers: List[_cabi.B2LayerDesc]
     n_ctx_train: int = 0
+    block_style: int = _cabi.B2_BLOCK_POSTSUM_LN
+    logit_scale: float = 1.0
 
 
 def _need(d: dict, key: str, where: str):
