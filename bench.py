@@ -489,6 +489,73 @@ def measured_peak_tflops():
         return 1590.0, "fallback (1.59 PFLOP/s)"
 
 
+def time_layered(eng, prompt, n_dec, warm, n_param, tfl, hbm):
+    """Prefill and decode timings of one layer-list engine: one prompt pass, single-token steps of one and of four sequences,
+    and the per-kernel-kind device time of one profiled prompt pass and one profiled single-token step. `n_param`: matrix
+    parameters a token passes through (for a mixture of experts: the chosen experts only)."""
+    from llama_cpp.kv_pages import SequenceSlots
+    n_prompt = len(prompt)
+    seqs = SequenceSlots(eng)
+    rec = {"params_per_token_matmul": n_param}
+    launches = 0
+
+    def prefill_once(key, profile=False):
+        seqs.open(key)
+        slot = seqs.extend(key, n_prompt)
+        eng.profile(profile)
+        eng.timer_start()
+        eng.step([(slot, prompt)], want=[[n_prompt - 1]])
+        ms = eng.timer_stop()
+        eng.profile(False)
+        return ms
+
+    for i in range(warm):
+        prefill_once(f"w{i}")
+        seqs.close(f"w{i}")
+    l0 = eng.launch_count()
+    ms = prefill_once("p0")
+    launches += eng.launch_count() - l0
+    rec["prefill_ms"], rec["prefill_tok_s"] = round(ms, 3), round(n_prompt / ms * 1e3, 1)
+    rec["prefill_tflops"] = round(2.0 * n_param * n_prompt / ms / 1e9, 1)
+    rec["prefill_frac_of_bf16_peak"] = round(rec["prefill_tflops"] / tfl, 3)
+    # decode: batch 1 (the sequence just prefilled), then 4 sequences per step
+    tok = [1]
+    for _ in range(3):
+        eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
+    eng.timer_start()
+    l0 = eng.launch_count()
+    for _ in range(n_dec):
+        eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
+    ms1 = eng.timer_stop() / n_dec
+    launches += eng.launch_count() - l0
+    rec["decode_bs1_ms"], rec["decode_bs1_tok_s"] = round(ms1, 4), round(1e3 / ms1, 1)
+    rec["decode_bs1_frac_of_hbm"] = round(2.0 * n_param / (ms1 * 1e-3) / 1e9 / hbm, 3)
+    for k in ("q1", "q2", "q3"):
+        prefill_once(k)
+    keys = ["p0", "q1", "q2", "q3"]
+    for _ in range(3):
+        eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
+    eng.timer_start()
+    for _ in range(n_dec):
+        eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
+    ms4 = eng.timer_stop() / n_dec
+    rec["decode_bs4_ms"], rec["decode_bs4_tok_s"] = round(ms4, 4), round(4e3 / ms4, 1)
+    for k in keys:
+        seqs.close(k)
+    prefill_once("prof", profile=True)
+    rec["prefill_kinds_ms"] = {k: round(v["ms"], 3) for k, v in eng.profile_read().items() if v["launches"]}
+    eng.profile(True)
+    eng.step([(seqs.extend("prof", 1), tok)], sample=[True])
+    rec["decode_kinds_ms"] = {k: round(v["ms"], 4) for k, v in eng.profile_read().items() if v["launches"]}
+    eng.profile(False)
+    return rec, launches
+
+
+def matrix_params(tensors, skip=("embed",)):
+    import numpy as np
+    return sum(int(np.prod(t.shape)) for k, t in tensors.items() if len(t.shape) == 2 and k not in skip)
+
+
 def goponex_workload(args):
     """Prefill and decode throughput of the Goponex layer-list graph at three layer sizes (random bf16 weights, four layers:
     mLSTM, 2 x attention+scan with feed-forward, mLSTM) beside the llama graph at equal width, depth and feed-forward size
@@ -497,7 +564,6 @@ def goponex_workload(args):
     from llama_cpp import goponex, synth
     from llama_cpp.engine import Engine, SamplingSettings
     from llama_cpp.gguf_file import GGUFFile
-    from llama_cpp.kv_pages import SequenceSlots
     hbm, hbm_src = measured_peak_gbs()
     tfl, tfl_src = measured_peak_tflops()
     n_prompt, n_dec, vocab = 2048, max(8, min(args.steps, 64)), 32000
@@ -510,63 +576,10 @@ def goponex_workload(args):
         width, heads, kv, ff, llama_arch = GOPONEX_SIZES[name]
         cfg, tensors = goponex.synthetic(width, heads, kv, ff, vocab)
         eng = goponex.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
-        n_param = sum(int(np.prod(t.shape)) for k, t in tensors.items() if len(t.shape) == 2 and k != "embed")
+        n_param = matrix_params(tensors)
         del tensors
-        seqs = SequenceSlots(eng)
-        rec = {"params_per_token_matmul": n_param}
-
-        def prefill_once(key, profile=False):
-            seqs.open(key)
-            slot = seqs.extend(key, n_prompt)
-            eng.profile(profile)
-            eng.timer_start()
-            eng.step([(slot, prompt)], want=[[n_prompt - 1]])
-            ms = eng.timer_stop()
-            eng.profile(False)
-            return ms
-
-        for i in range(max(3, args.warmup // 4)):
-            prefill_once(f"w{i}")
-            seqs.close(f"w{i}")
-        l0 = eng.launch_count()
-        ms = min(prefill_once(f"p{i}") or 1e9 for i in range(1))
-        launches += eng.launch_count() - l0
-        rec["prefill_ms"], rec["prefill_tok_s"] = round(ms, 3), round(n_prompt / ms * 1e3, 1)
-        rec["prefill_tflops"] = round(2.0 * n_param * n_prompt / ms / 1e9, 1)
-        rec["prefill_frac_of_bf16_peak"] = round(rec["prefill_tflops"] / tfl, 3)
-        # decode: batch 1 (the sequence just prefilled), then 4 sequences per step
-        tok = [1]
-        slot = seqs.slot("p0")
-        for _ in range(3):
-            eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
-        eng.timer_start()
-        l0 = eng.launch_count()
-        for _ in range(n_dec):
-            eng.step([(seqs.extend("p0", 1), tok)], sample=[True])
-        ms1 = eng.timer_stop() / n_dec
-        launches += eng.launch_count() - l0
-        w_bytes = 2.0 * n_param
-        rec["decode_bs1_ms"], rec["decode_bs1_tok_s"] = round(ms1, 4), round(1e3 / ms1, 1)
-        rec["decode_bs1_frac_of_hbm"] = round(w_bytes / (ms1 * 1e-3) / 1e9 / hbm, 3)
-        for k in ("q1", "q2", "q3"):
-            prefill_once(k)
-        keys = ["p0", "q1", "q2", "q3"]
-        for _ in range(3):
-            eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
-        eng.timer_start()
-        for _ in range(n_dec):
-            eng.step([(seqs.extend(k, 1), tok) for k in keys], sample=[True] * 4)
-        ms4 = eng.timer_stop() / n_dec
-        rec["decode_bs4_ms"], rec["decode_bs4_tok_s"] = round(ms4, 4), round(4e3 / ms4, 1)
-        # per-kernel-kind device time of one profiled prompt pass and one profiled single-token step
-        for k in keys:
-            seqs.close(k)
-        prefill_once("prof", profile=True)
-        rec["prefill_kinds_ms"] = {k: round(v["ms"], 3) for k, v in eng.profile_read().items() if v["launches"]}
-        eng.profile(True)
-        eng.step([(seqs.extend("prof", 1), tok)], sample=[True])
-        rec["decode_kinds_ms"] = {k: round(v["ms"], 4) for k, v in eng.profile_read().items() if v["launches"]}
-        eng.profile(False)
+        rec, nl = time_layered(eng, prompt, n_dec, max(3, args.warmup // 4), n_param, tfl, hbm)
+        launches += nl
         eng.close()
         # the llama graph at equal width / depth / feed-forward size
         path = ensure_model(llama_arch, "Q8_0")
@@ -613,14 +626,72 @@ def goponex_workload(args):
     return 0
 
 
+VAZUNEX_SIZES = {      # name: (width, heads, expert ff, experts, chosen per token; Goponex heads, kv heads, ff at equal width)
+    "1k": (1024, 8, 512, 16, 4, 8, 2, 4096),
+    "2k": (2048, 16, 1024, 16, 4, 16, 4, 8192),
+    "4k": (4096, 32, 2048, 16, 4, 32, 8, 14336),
+}
+
+
+def vazunex_workload(args):
+    """Prefill and decode throughput of the Vazunex layer-list graph at three layer sizes (random bf16 weights, four layers:
+    latent attention, delta rule, state-space, delta rule, each with a mixture of 16 experts + 2 identity slots, 4 chosen)
+    beside the Goponex graph (the closest existing model: the same engine, dense bf16 tensors, windowed attention +
+    recurrences) at equal width and depth. Device time with CUDA events around the engine calls."""
+    import numpy as np
+    from llama_cpp import goponex, vazunex
+    hbm, hbm_src = measured_peak_gbs()
+    tfl, tfl_src = measured_peak_tflops()
+    n_prompt, n_dec, vocab = 2048, max(8, min(args.steps, 64)), 32000
+    rng = np.random.default_rng(0)
+    prompt = [int(t) for t in rng.integers(0, vocab, size=n_prompt)]
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    out, launches = {}, 0
+    warm = max(3, args.warmup // 4)
+    for name in (args.sizes.split(",") if args.sizes else list(VAZUNEX_SIZES)):
+        width, heads, eff, n_exp, top, g_heads, g_kv, g_ff = VAZUNEX_SIZES[name]
+        cfg, tensors = vazunex.synthetic(width, heads, eff, vocab, experts=n_exp, top=top)
+        eng = vazunex.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
+        # a token passes through the shared matrices and through `top` of the experts (identity slots cost nothing)
+        n_expert = sum(int(np.prod(t.shape)) for k, t in tensors.items() if ".mlp.e" in k)
+        n_param = matrix_params(tensors) - n_expert + n_expert * top // n_exp
+        total = matrix_params(tensors)
+        del tensors
+        rec, nl = time_layered(eng, prompt, n_dec, warm, n_param, tfl, hbm)
+        rec["matrix_params_total"] = total
+        launches += nl
+        eng.close()
+        cfg, tensors = goponex.synthetic(width, g_heads, g_kv, g_ff, vocab)
+        eng = goponex.open_synthetic(cfg, tensors, n_ctx=n_prompt + 4 * n_dec + 64, max_seqs=4, dtype="bfloat16", max_step_tokens=n_prompt)
+        g_param = matrix_params(tensors)
+        del tensors
+        rec["goponex"], nl = time_layered(eng, prompt, n_dec, warm, g_param, tfl, hbm)
+        eng.close()
+        out[name] = rec
+    clocks = sampler.result()
+    last = out[list(out)[-1]]
+    line = {"metric": "vazunex_prefill_tokens_per_s", "value": last["prefill_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": n_dec, "warmup": warm, "ms_per_step": last["decode_bs1_ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": "Vazunex layer-list graph, 4 layers (latent attention, delta rule, state-space, delta rule; 16 experts + 2 identity slots, 4 chosen), random bf16 weights",
+                       "prompt_tokens": n_prompt, "decode_steps": n_dec, "global_batch": 1, "seq_len": n_prompt,
+                       "parallelism": "single GPU",
+                       "l2": "each step streams the weight set it uses (0.1-1 GB, larger than the 126 MB L2); no flush needed"},
+            "sizes": out, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tfl, "bf16_source": tfl_src},
+            "clocks": clocks, "gpu_launches": int(launches)}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS) + ["goponex-sizes"])
-    ap.add_argument("--sizes", default="", help="goponex-sizes: comma-separated subset of 1k,2k,4k (default all)")
+    ap.add_argument("--workload", default="llama3-8b-q4_k_m-bs1", choices=sorted(WORKLOADS) + ["goponex-sizes", "vazunex-sizes"])
+    ap.add_argument("--sizes", default="", help="goponex-sizes / vazunex-sizes: comma-separated subset of 1k,2k,4k (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity-check", action="store_true")
     ap.add_argument("--batch-extra", type=int, default=32, help="bs1 workloads: also time this many sequences per step (0 = skip)")
@@ -630,11 +701,11 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.workload == "goponex-sizes":
+    if args.workload in ("goponex-sizes", "vazunex-sizes"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no layer-list models (llama.cpp graphs only)"}))
             return 0
-        return goponex_workload(args)
+        return goponex_workload(args) if args.workload == "goponex-sizes" else vazunex_workload(args)
     arch, ftype, n_prompt, batch = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
