@@ -346,7 +346,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_s
 
 constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 64, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
 constexpr int BIG_SMEM = BIG_STAGES * (BIG_BM + BIG_BN) * BIG_LD * 2;
-__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, DenseDev a) {
+__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, int ldxb, DenseDev a) {
     griddep_launch();
     griddep_wait();
     extern __shared__ __align__(16) unsigned char big_smem[];
@@ -356,7 +356,8 @@ __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16*
     if (!dense_tile<__nv_bfloat16>(a, BIG_BM, x, w, y, aux, t0, T)) return;
     const int N = a.N, K = a.K;
     const int n0 = blockIdx.x * BIG_BN;
-    // the rounded copy holds the rows of the step (grouped: of the tokens, gathered here) as [row][K]
+    // the rounded copy holds the input rows as [row][ldxb] (grouped: gathered here; batched: batch b starts at column b * x_bs)
+    if (!a.grouped) xb += (long)blockIdx.z * a.x_bs;
     int my_rows[BIG_BK / 16];
 #pragma unroll
     for (int it = 0; it < BIG_BK / 16; it++) {
@@ -375,7 +376,7 @@ __global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16*
             const int k = k0 + kk;
             const int t = t0 + row, n = n0 + row;
             const bool ka = k < K;
-            cp_async_16(As + ((size_t)stage * BIG_BM + row) * BIG_LD + kk, xb + (size_t)my_rows[it] * K + (ka ? k : 0), (ka && t < T) ? 16 : 0);
+            cp_async_16(As + ((size_t)stage * BIG_BM + row) * BIG_LD + kk, xb + (size_t)my_rows[it] * ldxb + (ka ? k : 0), (ka && t < T) ? 16 : 0);
             cp_async_16(Bs + ((size_t)stage * BIG_BN + row) * BIG_LD + kk, w + (size_t)min(n, N - 1) * K + (ka ? k : 0), (ka && n < N) ? 16 : 0);
         }
     };
@@ -432,19 +433,37 @@ cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s) {
     d.scale = a.scale; d.aux = a.aux; d.ldaux = a.ldaux; d.x_bs = a.x_bs; d.w_bs = a.w_bs; d.y_bs = a.y_bs; d.aux_bs = a.aux_bs;
     if (a.groups) { d.g = *a.groups; d.grouped = a.groups->tile_group ? 2 : 1; }
     if (d.grouped == 1 || (!d.grouped && a.T <= ROWS_MAX_T)) return wb ? launch_rows<__nv_bfloat16>(d, a.batch, s) : launch_rows<float>(d, a.batch, s);
+    // few output columns in 32-bit (router scores): the tiled kernel would run a handful of CTAs over the whole K; the
+    // few-token kernel over chunks of 8 rows keeps every SM busy and streams the small matrix from L2
+    if (a.exact && !d.grouped && a.batch == 1 && a.N <= 64) {
+        const int chunks = a.T / ROWS_MAX_T, rem = a.T % ROWS_MAX_T;
+        DenseDev c = d;
+        c.T = ROWS_MAX_T; c.x_bs = (long)ROWS_MAX_T * a.ldx; c.y_bs = (long)ROWS_MAX_T * a.ldy; c.aux_bs = (long)ROWS_MAX_T * a.ldaux; c.w_bs = 0;
+        cudaError_t ce = wb ? launch_rows<__nv_bfloat16>(c, chunks, s) : launch_rows<float>(c, chunks, s);
+        if (ce != cudaSuccess || rem == 0) return ce;
+        c = d;
+        c.T = rem; c.x += (size_t)chunks * ROWS_MAX_T * a.ldx; c.y += (size_t)chunks * ROWS_MAX_T * a.ldy;
+        if (c.aux) c.aux += (size_t)chunks * ROWS_MAX_T * a.ldaux;
+        return wb ? launch_rows<__nv_bfloat16>(c, 1, s) : launch_rows<float>(c, 1, s);
+    }
     const unsigned gz = d.grouped ? 1 : a.batch;
-    // the large-tile kernel reads a rounded copy of the input rows [T][K]
-    const int x_rows_total = a.T;
-    if (wb && !a.exact && a.xb && a.batch == 1 && !d.grouped && a.T >= 64 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0) {
+    // The large-tile kernel reads a rounded copy of the input: [T][K]; batched: [T][x_span] with batch b at column b * x_bs;
+    // grouped (128-row tiles): [x_total_rows][K], gathered by the kernel.
+    const int x_rows_total = d.grouped ? a.groups->x_total_rows : a.T;
+    const int span = a.batch > 1 ? a.x_span : a.K;
+    const bool big_ok = wb && !a.exact && a.xb && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && span % 8 == 0 &&
+                        (a.batch == 1 || (a.x_span > 0 && a.x_bs % 8 == 0 && a.w_bs % 8 == 0));
+    if (d.grouped == 2 && a.groups->tile_max == BIG_BM && !big_ok) return cudaErrorInvalidValue;
+    if (big_ok && (d.grouped ? a.groups->tile_max == BIG_BM : a.T >= 64)) {
         static bool attr_done = false;
         if (!attr_done) { cudaFuncSetAttribute(dense_mma_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIG_SMEM); attr_done = true; }
-        const long pairs = (long)x_rows_total * (a.K / 2);
+        const long pairs = (long)x_rows_total * (span / 2);
         cudaError_t ce = launch_chain(rows_to_bf16_kernel, dim3((unsigned)std::min<long>((pairs + 255) / 256, 148 * 8)), dim3(256), 0, s,
-                                      a.x, a.ldx, x_rows_total, a.K, a.xb);
+                                      a.x, a.ldx, x_rows_total, span, a.xb);
         if (ce != cudaSuccess) return ce;
         const unsigned gy = d.grouped ? (unsigned)a.groups->max_tiles : (unsigned)((a.T + BIG_BM - 1) / BIG_BM);
-        return launch_chain(dense_mma_big_kernel, dim3((a.N + BIG_BN - 1) / BIG_BN, gy), dim3(256), (size_t)BIG_SMEM, s,
-                            (const __nv_bfloat16*)a.xb, d);
+        return launch_chain(dense_mma_big_kernel, dim3((a.N + BIG_BN - 1) / BIG_BN, gy, gz), dim3(256), (size_t)BIG_SMEM, s,
+                            (const __nv_bfloat16*)a.xb, span, d);
     }
     dim3 grid((a.N + 63) / 64, d.grouped ? (unsigned)a.groups->max_tiles : (unsigned)((a.T + 63) / 64), gz);
     if (wb && !a.exact) return launch_chain(dense_mma_kernel, grid, dim3(128), 0, s, d);

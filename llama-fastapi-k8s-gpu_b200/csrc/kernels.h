@@ -25,6 +25,14 @@ inline cudaError_t launch_chain(void (*k)(KArgs...), dim3 grid, dim3 block, size
     return cudaLaunchKernelEx(&cfg, k, std::forward<Args>(args)...);
 }
 
+// Launches inside this scope carry no dependent-launch attribute: the kernel starts when its predecessor has ended, so its
+// CTAs are spread over all SMs. For long-running latency-bound kernels with few CTAs (recurrences over a prompt).
+struct PlainLaunch {
+    bool prev;
+    PlainLaunch() : prev(g_chain_pdl) { g_chain_pdl = false; }
+    ~PlainLaunch() { g_chain_pdl = prev; }
+};
+
 // ---------------------------------------------------------------- mat-vec (matvec.cu)
 enum MvMode { MV_STORE = 0, MV_RESID = 1, MV_QKV = 2, MV_GATEUP = 3 };
 #ifndef B2_MV_NCW

@@ -252,7 +252,7 @@ int layered_finalize(b2_engine* e) {
     if (c.block_style == B2_BLOCK_PRENORM_RMS && (rc = vec_f32(e, m, "embed.norm", W, 1, &m->embed_norm))) return rc;
     const size_t cache_esz = m->exact ? 4 : 2;
     size_t max_proj = 1, max_buf = 1, max_ff = 1, max_attn = 0, max_attn_d = 0;
-    size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0;
+    size_t moe_pairs = 0, moe_slots = 0, moe_ff = 0, moe_experts = 0, moe_xb = 0;     // moe_xb: expert activations per step token
     for (int li = 0; li < c.n_layer; li++) {
         LyLayer& L = m->layers[li];
         const b2_layer_desc& d = L.d;
@@ -314,7 +314,8 @@ int layered_finalize(b2_engine* e) {
             if ((rc = dev_alloc(m, &L.la_pool, pool, true))) return rc;
             e->kv_bytes += (int64_t)pool;
             max_proj = std::max<size_t>(max_proj, L.la_proj.N);
-            max_buf = std::max<size_t>({max_buf, (size_t)H * Dk, (size_t)vd});
+            max_buf = std::max<size_t>({max_buf, (size_t)H * Dk, (size_t)H * dq, (size_t)vd});
+            max_attn = 1; max_attn_d = std::max<size_t>(max_attn_d, d.la_rank);
         } else if (d.mixer == B2_MIX_DELTA_RULE) {
             const std::string a = p + "mix.";
             const int H = d.mm_heads, G = d.key_heads, kd = G * d.mm_dim, vd = H * d.mm_vdim;
@@ -374,6 +375,7 @@ int layered_finalize(b2_engine* e) {
             moe_pairs = std::max<size_t>(moe_pairs, (size_t)Tm * d.moe_top);
             moe_slots = std::max<size_t>(moe_slots, slots);
             moe_ff = std::max<size_t>(moe_ff, d.n_ff);
+            moe_xb = std::max<size_t>(moe_xb, (size_t)d.moe_top * d.n_ff);
             moe_experts = std::max<size_t>(moe_experts, d.moe_experts);
         } else if (d.n_ff > 0) {
             if ((rc = vec_f32(e, m, p + "norm2", W, 1, &L.norm2))) return rc;
@@ -391,7 +393,7 @@ int layered_finalize(b2_engine* e) {
     if ((rc = dev_alloc(m, (void**)&m->oR, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->hn, (size_t)Tm * W * 4))) return rc;
     if ((rc = dev_alloc(m, (void**)&m->ff, (size_t)Tm * max_ff * 4))) return rc;
-    if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W}) * 2 + 64))) return rc;
+    if (!m->exact && (rc = dev_alloc(m, (void**)&m->xb, (size_t)(Tm + B2_STEP_MAX_ENTRIES) * std::max<size_t>({max_buf, max_ff, (size_t)W, moe_xb}) * 2 + 64))) return rc;
     if (max_attn > 0) {
         m->attn_split_floats = (int)(148 * 2 * (max_attn_d + 2));       // T * H * splits <= 2 * 148 on the split path
         if ((rc = dev_alloc(m, (void**)&m->attn_split, (size_t)m->attn_split_floats * 4))) return rc;
@@ -659,6 +661,7 @@ static int mix_latent_attn(b2_engine* e, LayeredModel* m, LyLayer& L, const Ragg
     a.pool = L.la_pool; a.cache_f32 = m->exact ? 1 : 0; a.block_tables = m->block_tables; a.block_tokens = c.kv_block_tokens;
     a.H = H; a.d = d.head_dim; a.dr = d.la_rot_dim; a.rank = d.la_rank; a.window = d.window > 0 ? d.window : c.n_ctx;
     a.scale = (float)d.attn_scale; a.eps = c.norm_eps; a.sink = L.sink; a.qv = m->buf[0]; a.o_lat = m->buf[1];
+    a.split_scratch = m->attn_split; a.split_capacity = m->attn_split_floats;
     {
         StepProfiler sp(m, st, 2);
         CK(latent_store_launch(a, r, st));
@@ -666,16 +669,16 @@ static int mix_latent_attn(b2_engine* e, LayeredModel* m, LyLayer& L, const Ragg
     }
     // every head's unrotated query through its transposed key map: the head's query in the latent's coordinates
     DenseArgs b = {};
-    b.batch = H; b.x_bs = dq; b.w_bs = (long)d.la_rank * d.head_dim; b.y_bs = Dk;
+    b.batch = H; b.x_bs = dq; b.w_bs = (long)d.la_rank * d.head_dim; b.y_bs = Dk; b.x_span = H * dq;
     if ((rc = dense(e, m, L.uk_t, m->proj + L.q_off, Np, m->buf[0], H * Dk, T, nullptr, EPI_NONE, 1, &b))) return rc;
     {
         StepProfiler sp(m, st, 2);
         CK(latent_attn_launch(a, r, st));
-        e->launches++;
+        e->launches += 2;
     }
     // values of the weighted latent sums, head by head, times the sigmoid output gate
     DenseArgs v = {};
-    v.batch = H; v.x_bs = d.la_rank; v.w_bs = (long)d.la_vdim * d.la_rank; v.y_bs = d.la_vdim;
+    v.batch = H; v.x_bs = d.la_rank; v.w_bs = (long)d.la_vdim * d.la_rank; v.y_bs = d.la_vdim; v.x_span = H * d.la_rank;
     v.aux = m->proj + L.g_off; v.ldaux = Np; v.aux_bs = d.la_vdim;
     if ((rc = dense(e, m, L.uv, m->buf[1], H * d.la_rank, m->buf[2], H * d.la_vdim, T, nullptr, EPI_MUL_SIGMOID, 1, &v))) return rc;
     return dense(e, m, L.attn_o, m->buf[2], H * d.la_vdim, m->oL, W, T);
@@ -765,7 +768,7 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     const int T = r.T, W = m->c.n_embd, slots = d.moe_experts + d.moe_identity, pairs = T * d.moe_top, ff = d.n_ff;
     int rc;
     DenseArgs ex = {};
-    ex.exact = true;                               // router scores are 32-bit products
+    ex.exact = true;                               // router scores are 32-bit products in both modes
     if ((rc = dense(e, m, L.router, in, W, m->moe_logits, slots, T, nullptr, EPI_NONE, 7, &ex))) return rc;
     MoeRouteArgs ra = {};
     ra.logits = m->moe_logits; ra.ld = slots; ra.correction = L.correction; ra.n_slots = slots; ra.n_experts = d.moe_experts;
@@ -774,27 +777,30 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     DenseGroups g = {};
     g.n_groups = d.moe_experts;
     const bool tiled = T > 8;
+    // long prompts in the serving mode: 128-row tiles through the large tensor-core kernel
+    const bool big = tiled && !m->exact && L.gate_up.type == T_BF16 && pairs >= 1024 && W % 8 == 0 && ff % 8 == 0 && m->xb;
+    g.tile_max = big ? 128 : 64;
     {
         StepProfiler sp(m, st, 7);
         CK(moe_route_launch(ra, T, st));
         e->launches++;
         if (tiled) {
             MoeSortArgs sa = {};
-            sa.sel = m->moe_sel; sa.n_pairs = pairs; sa.top = d.moe_top; sa.n_experts = d.moe_experts; sa.pos = m->moe_pos; sa.x_rows = m->moe_rows;
+            sa.sel = m->moe_sel; sa.n_pairs = pairs; sa.top = d.moe_top; sa.n_experts = d.moe_experts; sa.tile = g.tile_max; sa.pos = m->moe_pos; sa.x_rows = m->moe_rows;
             sa.n_tiles = m->moe_tiles; sa.tile_group = m->moe_tiles + 1; sa.tile_row0 = sa.tile_group + m->moe_max_tiles;
             sa.tile_rows = sa.tile_row0 + m->moe_max_tiles; sa.max_tiles = m->moe_max_tiles;
             CK(moe_sort_launch(sa, st));
             e->launches++;
             g.tile_group = sa.tile_group; g.tile_row0 = sa.tile_row0; g.tile_rows = sa.tile_rows; g.n_tiles = sa.n_tiles;
-            g.max_tiles = std::min(m->moe_max_tiles, pairs / 64 + d.moe_experts + 1);
+            g.max_tiles = std::min(m->moe_max_tiles, pairs / g.tile_max + d.moe_experts + 1);
         } else g.group = m->moe_sel;
     }
     DenseArgs up = {};
-    g.x_rows = tiled ? m->moe_rows : m->moe_tok; g.w_stride = (long)2 * ff * W;
+    g.x_rows = tiled ? m->moe_rows : m->moe_tok; g.w_stride = (long)2 * ff * W; g.x_total_rows = T;
     up.groups = &g;
     if ((rc = dense(e, m, L.gate_up, in, W, m->moe_h, ff, pairs, nullptr, EPI_GLU_SILU, 1, &up))) return rc;
     DenseGroups g2 = g;
-    g2.x_rows = nullptr; g2.w_stride = (long)W * ff;
+    g2.x_rows = nullptr; g2.w_stride = (long)W * ff; g2.x_total_rows = pairs;
     DenseArgs dn = {};
     dn.groups = &g2;
     if ((rc = dense(e, m, L.e_down, m->moe_h, ff, m->moe_y, W, pairs, nullptr, EPI_NONE, 1, &dn))) return rc;

@@ -47,6 +47,8 @@ struct DenseGroups {
     int n_groups = 0;
     long w_stride = 0;                 // elements between the matrices of two groups
     int max_tiles = 0;                 // grid size of a tiled launch
+    int tile_max = 64;                 // most rows of a tile: 64, or 128 (large tensor-core tiles; bf16 serving mode only)
+    int x_total_rows = 0;              // rows of the input matrix (128-row tiles: it is rounded to bf16 as a whole first)
 };
 struct DenseArgs {
     const float* x; int ldx;
@@ -61,6 +63,7 @@ struct DenseArgs {
     const float* aux = nullptr; int ldaux = 0;      // EPI_MUL_SIGMOID
     // batch > 1: `batch` independent products, operand b at x + b * x_bs, w + b * w_bs (elements), y + b * y_bs, aux + b * aux_bs
     int batch = 1; long x_bs = 0, w_bs = 0, y_bs = 0, aux_bs = 0;
+    int x_span = 0;                 // batch > 1: columns of x that hold all batches' inputs (for the rounded copy), or 0
     const DenseGroups* groups = nullptr;            // grouped product (T = number of pair rows)
 };
 cudaError_t dense_launch(const DenseArgs& a, cudaStream_t s);
@@ -205,6 +208,8 @@ struct LatentAttnArgs {
     const float* sink;                                // [H]
     float* qv;                                        // [T][H][rank + dr]; the first `rank` of each head are filled by the caller
     float* o_lat;                                     // [T][H][rank]
+    float* split_scratch;      // few-token steps: partial (max, sum, output) per key range, [T][H][splits][rank + 2]
+    int split_capacity;        // floats in split_scratch
 };
 // norm of c, rotation of the shared key part, both into the pages; rotated query parts into qv
 cudaError_t latent_store_launch(const LatentAttnArgs& a, const RaggedDev& r, cudaStream_t s);
@@ -220,10 +225,10 @@ struct MoeRouteArgs {
     int* pair_token;                       // [T][top]: t (the input row of each pair)
 };
 cudaError_t moe_route_launch(const MoeRouteArgs& a, int T, cudaStream_t s);
-// pairs sorted by expert into 64-row tiles: pos[p] = row of pair p in the sorted order (-1: identity slot), x_rows[row] =
+// pairs sorted by expert into tiles of `tile` rows: pos[p] = row of pair p in the sorted order (-1: identity slot), x_rows[row] =
 // token of that row, and the tile table; all in device memory (meta: [0] = number of tiles)
 struct MoeSortArgs {
-    const int* sel; int n_pairs, top, n_experts;
+    const int* sel; int n_pairs, top, n_experts, tile;      // tile: rows per tile
     int* pos; int* x_rows; int* tile_group; int* tile_row0; int* tile_rows; int* n_tiles; int max_tiles;
 };
 cudaError_t moe_sort_launch(const MoeSortArgs& a, cudaStream_t s);

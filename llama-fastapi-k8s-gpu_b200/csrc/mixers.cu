@@ -786,6 +786,7 @@ __global__ void __launch_bounds__(256) scan_recurrence_lanes_kernel(ScanArgs a, 
 
 cudaError_t scan_recurrence_launch(const ScanArgs& a, const RaggedDev& r, cudaStream_t s) {
     if (a.N > SCAN_MAXS * 32) return cudaErrorInvalidValue;
+    PlainLaunch pl;        // latency-bound over the prompt: CTAs spread over all SMs (see kernels.h)
     if (a.N <= 32) {
         const long n = (long)r.T * a.inner;
         cudaError_t ce = launch_chain(scan_prepare_kernel, dim3((unsigned)std::min<long>((n + 255) / 256, 148 * 8)), dim3(256), 0, s, a, r.T);
@@ -972,7 +973,10 @@ cudaError_t matrix_mem_launch(const MatrixMemArgs& a, const RaggedDev& r, cudaSt
     if (!attr_done) { cudaFuncSetAttribute(matrix_mem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); attr_done = true; }
     cudaError_t ce = launch_chain(matrix_mem_gates_kernel, dim3((r.T * a.H + 127) / 128), dim3(128), 0, s, a, r.T);
     if (ce != cudaSuccess) return ce;
-    ce = launch_chain(matrix_mem_kernel, dim3(r.n_seg, a.H, (a.dv + MM_COLS - 1) / MM_COLS), dim3(std::max(RG * MM_COLS, 64)), smem, s, a, r, RG);
+    {
+        PlainLaunch pl;    // latency-bound over the prompt: CTAs spread over all SMs (see kernels.h)
+        ce = launch_chain(matrix_mem_kernel, dim3(r.n_seg, a.H, (a.dv + MM_COLS - 1) / MM_COLS), dim3(std::max(RG * MM_COLS, 64)), smem, s, a, r, RG);
+    }
     if (ce != cudaSuccess) return ce;
     return launch_chain(matrix_mem_out_kernel, dim3(r.T, a.H), dim3(128), 0, s, a);
 }

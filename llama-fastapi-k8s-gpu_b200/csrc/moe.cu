@@ -80,10 +80,9 @@ cudaError_t moe_route_launch(const MoeRouteArgs& a, int T, cudaStream_t s) {
     return launch_chain(moe_route_kernel, dim3(T), dim3(32), smem, s, a);
 }
 
-// One CTA: histogram of the pairs by expert, tile table (64 rows a tile), placement. Which row of an expert's range a pair
+// One CTA: histogram of the pairs by expert, tile table, placement. Which row of an expert's range a pair
 // gets depends on the order of the atomics, but every output row is computed from its own input row alone, so the
 // order changes no number.
-constexpr int MOE_TILE = 64;
 __global__ void __launch_bounds__(1024) moe_sort_kernel(MoeSortArgs a) {
     griddep_launch();
     griddep_wait();
@@ -102,8 +101,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(MoeSortArgs a) {
         int rows = 0, tiles = 0;
         for (int e = 0; e < a.n_experts; e++) {
             offset[e] = rows;
-            for (int r0 = 0; r0 < count[e] && tiles < a.max_tiles; r0 += MOE_TILE, tiles++) {
-                a.tile_group[tiles] = e; a.tile_row0[tiles] = rows + r0; a.tile_rows[tiles] = min(MOE_TILE, count[e] - r0);
+            for (int r0 = 0; r0 < count[e] && tiles < a.max_tiles; r0 += a.tile, tiles++) {
+                a.tile_group[tiles] = e; a.tile_row0[tiles] = rows + r0; a.tile_rows[tiles] = min(a.tile, count[e] - r0);
             }
             rows += count[e];
         }

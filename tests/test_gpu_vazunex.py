@@ -202,12 +202,12 @@ def _peaky_latent_model(tmp_path, window):
     is parallel to the query and scores as high as the token's own key, far above the random rest; the rotated part is small.
     The score scale is low enough that the token's own key, the copy, the sink and the rest all hold a visible share."""
     H, d = 2, 32
-    cfg = vu.config([vu.latent(heads=H, dim=d, rot_dim=4, vdim=24, rank=d, window=window, scale=0.08)], width=64)
+    cfg = vu.config([vu.latent(heads=H, dim=d, rot_dim=16, vdim=24, rank=d, window=window, scale=0.08)], width=64)
     w = vu.random_weights(cfg, seed=5)
-    q = w["l0.mix.q"].reshape(H, d + 4, -1).copy()
+    q = w["l0.mix.q"].reshape(H, d + 16, -1).copy()
     q[:, :d, :] = w["l0.mix.dkv"][:d] * 1.5
     q[:, d:, :] *= 0.1
-    w["l0.mix.q"] = vu.bf16_round(q.reshape(H * (d + 4), -1))
+    w["l0.mix.q"] = vu.bf16_round(q.reshape(H * (d + 16), -1))
     w["l0.mix.uk"] = vu.bf16_round(np.tile(np.eye(d), (H, 1)))
     w["l0.mix.dkv.norm"] = vu.bf16_round(np.ones(d))
     w["l0.mix.sink"] = vu.bf16_round(np.array([3.0, 4.0]))
@@ -300,6 +300,28 @@ def test_far_token_through_the_recurrent_state(native_lib, tmp_path, kind):
     got = run_cut(eng, SequenceSlots(eng), "far", toks, [257, 64, 1, 2])
     eng.close()
     assert vu.rel_err(got[n - 1], true) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [16, 64, 100, 1000])
+def test_prompt_tiles(native_lib, tmp_path, window, dtype):
+    """Sizes the tensor-core prompt kernels take: a latent wider than one 128-column output chunk, windows narrower and wider
+    than the 64-query tile, enough (token, expert) pairs for 128-row expert tiles; a 300-token prompt at once and in portions
+    that straddle the tiles."""
+    from llama_cpp.kv_pages import SequenceSlots
+    mlp = vu.moe(experts=6, identity=0, top=4, ff=16, groups=(2, 2))
+    cfg = vu.config([vu.latent(mlp=mlp, heads=4, dim=16, rot_dim=16, vdim=32, rank=144, window=window),
+                     vu.latent(mlp=None, heads=2, dim=48, rot_dim=32, vdim=16, rank=32, window=window), vu.delta(mlp=mlp, dim=16, vdim=16)], width=64)
+    w = vu.random_weights(cfg, seed=13, ranks=(8, 16))
+    eng = open_engine(vu.write_model(str(tmp_path / "m"), cfg, w), dtype)
+    toks = tokens_for(cfg, 300, 14)
+    want = ref.forward(cfg, w, toks)
+    seqs = SequenceSlots(eng)
+    whole = run_cut(eng, seqs, "w", toks, [300])
+    parts = run_cut(eng, seqs, "p", toks, [100, 7, 64, 129])
+    eng.close()
+    assert close(whole, want, dtype)
+    assert close(parts, want, dtype)
 
 
 def test_steps_larger_than_the_engine_takes_at_once(hybrid):
