@@ -414,6 +414,23 @@ def test_sizes_that_are_one_odd_or_large(native_lib, tmp_path, dtype):
     assert close(got, ref.forward(cfg, w, toks), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [45, 50])
+def test_widths_no_vector_path_takes(native_lib, tmp_path, width, dtype):
+    """A model width that is odd, or even but no multiple of four: every product over the width takes its scalar path, in
+    prompts (tiles) and in few-token steps (rows); no mask entry (full causal attention); full attention over page borders."""
+    from llama_cpp.kv_pages import SequenceSlots
+    la = vu.latent(mlp=vu.moe(experts=4, identity=1, top=2, ff=10, groups=None), heads=2, dim=12, rot_dim=4, vdim=10, rank=18)
+    del la["mixer"]["mask"]
+    cfg = vu.config([la, vu.delta(mlp=vu.moe(ff=7)), vu.ssd(mlp=vu.moe(experts=2, identity=0, top=1, groups=None, ff=12))], width=width, vocab=77)
+    w = vu.random_weights(cfg, seed=21, ranks=(3, 9))
+    eng = open_engine(vu.write_model(str(tmp_path / "m"), cfg, w), dtype)
+    toks = tokens_for(cfg, 150, 22)
+    got = run_cut(eng, SequenceSlots(eng), "x", toks, [70, 1, 3, 20, 1])
+    eng.close()
+    assert close(got, ref.forward(cfg, w, toks), dtype)
+
+
 def test_greedy_generation_through_llama_and_the_scheduler(hybrid):
     """`Llama(model_path=<folder>)`: three callers at once, prompts of different lengths, greedy. Every generated token is
     the oracle's argmax for the sequence so far wherever the oracle's top-two margin is clear."""
