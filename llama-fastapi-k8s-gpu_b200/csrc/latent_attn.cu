@@ -142,11 +142,12 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(LatentAttnArgs a, int
 }
 
 // Tensor-core prompt kernel (bf16 pages, rank and rank + dr multiples of 16): a CTA takes one tile of up to 64 consecutive
-// queries of a segment, one head and one chunk of LT_DV latent columns of the output; 4 warps x 16 query rows; cached rows in
+// queries of a segment, one head and one chunk of LT_DV latent columns of the output (128 for latents up to 128 wide, else
+// 256: every chunk recomputes the scores, so wide chunks pay back their registers); 4 warps x 16 query rows; cached rows in
 // blocks of 64, staged in shared memory once for all 64 queries. S = Q K^T over the whole row, O += P K[:, chunk], with
 // mma.sync m16n8k16 (bf16 in, f32 accumulate); mask, running maximum, exponentials and sums are 32-bit; the running state
 // starts at (maximum = sink, sum = 1).
-constexpr int LT_Q = 64, LT_K = 64, LT_DV = 128;
+constexpr int LT_Q = 64, LT_K = 64;
 namespace {
 __device__ __forceinline__ void cp_async_16z(void* smem_dst, const void* gsrc, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
@@ -167,6 +168,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 }  // namespace
 
+template <int LT_DV>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentAttnArgs a, RaggedDev r) {
     griddep_launch();
     griddep_wait();
@@ -295,9 +297,14 @@ cudaError_t latent_attn_launch(const LatentAttnArgs& a, const RaggedDev& r, cuda
     static const bool no_mma = getenv("B2_NO_ATTN_MMA") != nullptr;        // tuning aid: scalar attention for prompts too
     if (!no_mma && !a.cache_f32 && r.T > 8 && a.rank % 16 == 0 && Dk % 16 == 0) {
         static bool attr_done = false;
-        if (!attr_done) { cudaFuncSetAttribute(latent_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 64 * (640 + 8) * 2); attr_done = true; }
+        if (!attr_done) {
+            cudaFuncSetAttribute(latent_attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 64 * (640 + 8) * 2);
+            cudaFuncSetAttribute(latent_attn_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 64 * (640 + 8) * 2);
+            attr_done = true;
+        }
         const size_t smem = (size_t)2 * 64 * (Dk + 8) * 2;
-        return launch_chain(latent_attn_mma_kernel, dim3(r.n_tiles, a.H, (a.rank + LT_DV - 1) / LT_DV), dim3(128), smem, s, a, r);
+        if (a.rank <= 128) return launch_chain(latent_attn_mma_kernel<128>, dim3(r.n_tiles, a.H, 1), dim3(128), smem, s, a, r);
+        return launch_chain(latent_attn_mma_kernel<256>, dim3(r.n_tiles, a.H, (a.rank + 255) / 256), dim3(128), smem, s, a, r);
     }
     // a step of a few tokens does not fill the GPU with one CTA per (token, head): split the keys (up to 16 ranges)
     int splits = 1;

@@ -305,13 +305,13 @@ def test_far_token_through_the_recurrent_state(native_lib, tmp_path, kind):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("window", [16, 64, 100, 1000])
 def test_prompt_tiles(native_lib, tmp_path, window, dtype):
-    """Sizes the tensor-core prompt kernels take: a latent wider than one 128-column output chunk, windows narrower and wider
+    """Sizes the tensor-core prompt kernels take: latents wider than 128 and than one 256-column output chunk, windows narrower and wider
     than the 64-query tile, enough (token, expert) pairs for 128-row expert tiles; a 300-token prompt at once and in portions
     that straddle the tiles."""
     from llama_cpp.kv_pages import SequenceSlots
     mlp = vu.moe(experts=6, identity=0, top=4, ff=16, groups=(2, 2))
     cfg = vu.config([vu.latent(mlp=mlp, heads=4, dim=16, rot_dim=16, vdim=32, rank=144, window=window),
-                     vu.latent(mlp=None, heads=2, dim=48, rot_dim=32, vdim=16, rank=32, window=window), vu.delta(mlp=mlp, dim=16, vdim=16)], width=64)
+                     vu.latent(mlp=None, heads=2, dim=48, rot_dim=32, vdim=16, rank=272, window=window), vu.delta(mlp=mlp, dim=16, vdim=16)], width=64)
     w = vu.random_weights(cfg, seed=13, ranks=(8, 16))
     eng = open_engine(vu.write_model(str(tmp_path / "m"), cfg, w), dtype)
     toks = tokens_for(cfg, 300, 14)
