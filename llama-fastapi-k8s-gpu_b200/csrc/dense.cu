@@ -346,7 +346,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_s
 
 constexpr int BIG_BM = 128, BIG_BN = 128, BIG_BK = 64, BIG_LD = BIG_BK + 8, BIG_STAGES = 3;
 constexpr int BIG_SMEM = BIG_STAGES * (BIG_BM + BIG_BN) * BIG_LD * 2;
-__global__ void __launch_bounds__(256) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, int ldxb, DenseDev a) {
+__global__ void __launch_bounds__(256, 2) dense_mma_big_kernel(const __nv_bfloat16* __restrict__ xb, int ldxb, DenseDev a) {
     griddep_launch();
     griddep_wait();
     extern __shared__ __align__(16) unsigned char big_smem[];
