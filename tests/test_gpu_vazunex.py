@@ -431,6 +431,66 @@ def test_widths_no_vector_path_takes(native_lib, tmp_path, width, dtype):
     assert close(got, ref.forward(cfg, w, toks), dtype)
 
 
+def random_config(seed):
+    """A random model: layer count and order, every size and constant drawn anew (sizes of the scale small real models have)."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(rng.integers(0, len(xs)))]
+
+    def mixture():
+        if rng.random() < 0.15:
+            return None
+        count = pick(1, 2, 3, 4)
+        per = pick(2, 3, 4, 6)
+        identity = pick(0, 0, 1, 2, 3)
+        identity = min(identity, count * per - 1)
+        keep = int(rng.integers(1, count + 1))
+        top = int(rng.integers(1, min(keep * per, 6) + 1))
+        return vu.moe(experts=count * per - identity, identity=identity, top=top, ff=pick(8, 24, 40, 64, 72),
+                      groups=None if count == 1 and rng.random() < 0.5 else (count, keep), scale=float(rng.uniform(0.5, 2.5)))
+
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        kind = pick("latent", "delta", "ssd")
+        if kind == "latent":
+            rot_dim = pick(4, 8, 16, 32)
+            layers.append(vu.latent(mlp=mixture(), heads=pick(1, 2, 4, 5, 8), dim=pick(16, 32, 48, 64, 96), rot_dim=rot_dim, vdim=pick(16, 32, 48, 80),
+                                    rank=pick(32, 64, 96, 160, 192, 272), window=pick(1, 7, 24, 40, 64, 65, 100, 129, 300),
+                                    base=pick(1e4, 5e5, 1e6), rot_dims=pick(rot_dim, rot_dim, rot_dim // 2)))
+        elif kind == "delta":
+            g = pick(1, 2, 3, 4)
+            layers.append(vu.delta(mlp=mixture(), heads=g * pick(1, 1, 2), kv_heads=g, dim=pick(16, 32, 48, 64, 96, 128), vdim=pick(16, 32, 48, 64, 100),
+                                   conv=pick(2, 3, 4, 5)))
+        else:
+            g = pick(1, 1, 2)
+            heads = g * pick(1, 2, 4, 5)
+            vdim = pick(16, 32, 48, 64)
+            parts = pick(1, 1, 2, heads)
+            layers.append(vu.ssd(mlp=mixture(), heads=heads, groups=g, vdim=vdim, state=pick(16, 32, 48, 64, 128), norm_groups=parts, conv=pick(2, 3, 4)))
+    cfg = vu.config(layers, width=pick(64, 96, 128, 192, 200, 320), vocab=pick(97, 256, 500), mult=float(rng.uniform(0.2, 1.0)),
+                    eps=pick(1e-5, 1e-6), logit_scale=float(rng.uniform(0.5, 3.0)))
+    return cfg, (pick(4, 8, 24, 32), pick(4, 8, 24, 32))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(native_lib, tmp_path, seed):
+    """Eight models nobody chose: each runs a 330-token prompt at once and in uneven portions with decoded tokens at the end,
+    in both modes, from a pool that forces page reuse."""
+    from llama_cpp.kv_pages import SequenceSlots
+    cfg, ranks = random_config(100 + seed)
+    w = vu.random_weights(cfg, seed=seed, ranks=ranks)
+    path = vu.write_model(str(tmp_path / "m"), cfg, w)
+    toks = tokens_for(cfg, 330, seed)
+    want = ref.forward(cfg, w, toks)
+    for dtype in ("float32", "bfloat16"):
+        eng = open_engine(path, dtype, n_ctx=384, max_seqs=2, kv_tokens=384 + 128)
+        seqs = SequenceSlots(eng)
+        whole = run_cut(eng, seqs, "w", toks, [330])
+        parts = run_cut(eng, seqs, "p", toks, [61, 3, 128, 2, 70, 37] + [1] * 29)
+        eng.close()
+        assert close(whole, want, dtype), (seed, dtype, "whole")
+        assert close(parts, want, dtype), (seed, dtype, "parts")
+
+
 def test_greedy_generation_through_llama_and_the_scheduler(hybrid):
     """`Llama(model_path=<folder>)`: three callers at once, prompts of different lengths, greedy. Every generated token is
     the oracle's argmax for the sequence so far wherever the oracle's top-two margin is clear."""
