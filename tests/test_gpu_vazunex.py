@@ -491,6 +491,53 @@ def test_random_configurations(native_lib, tmp_path, seed):
         assert close(parts, want, dtype), (seed, dtype, "parts")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(hybrid, tmp_path, dtype):
+    """`bin/trace_run` as a user starts it: six requests, at most four live, portions of some beside single tokens of others, a
+    request that sits out steps, a pool of --max-tokens sized for the live ones only, so pages and slots are used again; every
+    written row against the oracle."""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg, w, path = hybrid
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    reqs = {f"r{i}": tokens_for(cfg, n, 90 + i) for i, n in enumerate([130, 7, 64, 201, 33, 90])}
+    plans = {"r0": [64, 2, 1, 1, 40, 1], "r1": [1, 1], "r2": [3, 61], "r3": [100, 1, 1, 64, 2], "r4": [33], "r5": [2, 1, 50, 1]}
+    order, live, at, turn, steps, wanted = list(reqs), [], {k: 0 for k in reqs}, {k: 0 for k in reqs}, [], []
+    most = 0
+    while order or live:
+        while order and len(live) < 4:
+            live.append(order.pop(0))
+        entries, end = [], []
+        for k in list(live):
+            if k == "r3" and len(steps) % 3 == 1:          # sits this step out
+                continue
+            n = min(plans[k][turn[k] % len(plans[k])], len(reqs[k]) - at[k])
+            turn[k] += 1
+            want = sorted({0, n - 1})
+            entries.append({"id": k, "tokens": reqs[k][at[k]:at[k] + n], "want": want})
+            wanted.append((len(steps), k, [at[k] + x for x in want]))
+            at[k] += n
+        most = max(most, sum((at[k] + 63) // 64 * 64 for k in live))
+        for k in list(live):
+            if at[k] == len(reqs[k]):
+                end.append(k)
+                live.remove(k)
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(most)], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.split("\n") if ln.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    refs = {k: ref.forward(cfg, w, t) for k, t in reqs.items()}
+    for i in range(len(steps)):
+        rows = [(k, pos) for st, k, ps in wanted if st == i for pos in ps]
+        got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])
+        expect = np.stack([refs[k][pos] for k, pos in rows])
+        assert close(got, expect, dtype) if len(rows) >= 20 else vu.rel_err(got, expect) < (TOL[dtype] if dtype == "float32" else 0.2), i
+
+
 def test_greedy_generation_through_llama_and_the_scheduler(hybrid):
     """`Llama(model_path=<folder>)`: three callers at once, prompts of different lengths, greedy. Every generated token is
     the oracle's argmax for the sequence so far wherever the oracle's top-two margin is clear."""
