@@ -44,7 +44,7 @@ struct LyLayer {
     float *c_norm = nullptr, *sink = nullptr;
     void* la_pool = nullptr;
     // delta rule (st_proj rows q | k | v | b | a1 | g1) and state-space layer (st_proj rows z | x | B | C | dt)
-    DenseW st_proj, a2, g2, st_o;
+    DenseW st_proj, a2, g2, ag, st_o;                      // ag: a2 and g2 as one block-diagonal matrix over the input a1 | g1
     int v_off = 0, b_off = 0, a1_off = 0, g1_off = 0, dt_off = 0, conv_off = 0, conv_C = 0;
     float *st_conv_w = nullptr, *st_conv_b = nullptr, *st_conv_state = nullptr, *st_A_log = nullptr, *st_dt_bias = nullptr,
           *st_D = nullptr, *st_norm = nullptr, *st_state = nullptr;
@@ -326,6 +326,15 @@ int layered_finalize(b2_engine* e) {
             if ((rc = concat_f32(e, m, {{a + "q.conv", kd}, {a + "k.conv", kd}, {a + "v.conv", vd}}, d.conv_taps, &L.st_conv_w))) return rc;
             if ((rc = matrix(e, a + "a2", H * d.mm_dim, d.rank_a, L.a2))) return rc;
             if ((rc = matrix(e, a + "g2", vd, d.rank_g, L.g2))) return rc;
+            if (L.a2.type == L.g2.type) {      // one product for both second steps: zeros off the diagonal blocks add nothing
+                const size_t esz = L.a2.type == T_BF16 ? 2 : 4;
+                const int Ka = d.rank_a, Kg = d.rank_g, Kt = Ka + Kg, Na = H * d.mm_dim;
+                void* bd = nullptr;
+                if ((rc = dev_alloc(m, &bd, (size_t)(Na + vd) * Kt * esz + 64, true))) return rc;
+                CK(cudaMemcpy2DAsync(bd, Kt * esz, L.a2.w, Ka * esz, Ka * esz, Na, cudaMemcpyDeviceToDevice, e->stream));
+                CK(cudaMemcpy2DAsync((char*)bd + ((size_t)Na * Kt + Ka) * esz, Kt * esz, L.g2.w, Kg * esz, Kg * esz, vd, cudaMemcpyDeviceToDevice, e->stream));
+                L.ag.w = bd; L.ag.type = L.a2.type; L.ag.N = Na + vd; L.ag.K = Kt;
+            }
             if ((rc = vec_f32(e, m, a + "A_log", H, 1, &L.st_A_log))) return rc;
             if ((rc = vec_f32(e, m, a + "dt_bias", H * d.mm_dim, 1, &L.st_dt_bias))) return rc;
             if ((rc = vec_f32(e, m, a + "norm", d.mm_vdim, 1, &L.st_norm))) return rc;
@@ -333,7 +342,7 @@ int layered_finalize(b2_engine* e) {
             if ((rc = dev_alloc(m, (void**)&L.st_conv_state, (size_t)S * std::max(1, d.conv_taps - 1) * L.conv_C * 4, true))) return rc;
             if ((rc = dev_alloc(m, (void**)&L.st_state, (size_t)S * col_state_floats(H, d.mm_dim, d.mm_vdim) * 4, true))) return rc;
             max_proj = std::max<size_t>(max_proj, L.st_proj.N);
-            max_buf = std::max<size_t>({max_buf, (size_t)L.conv_C, (size_t)H * d.mm_dim, (size_t)vd});
+            max_buf = std::max<size_t>({max_buf, (size_t)L.conv_C, (size_t)H * d.mm_dim + vd});
         } else if (d.mixer == B2_MIX_SSD) {
             const std::string a = p + "mix.";
             const int H = d.mm_heads, inner = H * d.mm_vdim, gn = d.key_heads * d.d_state;
@@ -700,19 +709,28 @@ static int mix_delta_rule(b2_engine* e, LayeredModel* m, LyLayer& L, const Ragge
         CK(causal_conv_advance_launch(cv, r, st));
         e->launches += d.conv_taps > 1 ? 2 : 1;
     }
-    if ((rc = dense(e, m, L.a2, m->proj + L.a1_off, Np, m->buf[1], H * d.mm_dim, T))) return rc;
-    if ((rc = dense(e, m, L.g2, m->proj + L.g1_off, Np, m->buf[2], vd, T))) return rc;
+    // decays [T][H*dim] and gate inputs [T][H*vdim]: side by side in buf[1] (one product), or in buf[1] and buf[2]
+    float *a_out = m->buf[1], *g_out = m->buf[2];
+    int ld_a = H * d.mm_dim, ld_g = vd;
+    if (L.ag.w && L.g1_off == L.a1_off + d.rank_a) {
+        g_out = m->buf[1] + H * d.mm_dim;
+        ld_a = ld_g = H * d.mm_dim + vd;
+        if ((rc = dense(e, m, L.ag, m->proj + L.a1_off, Np, m->buf[1], ld_a, T))) return rc;
+    } else {
+        if ((rc = dense(e, m, L.a2, m->proj + L.a1_off, Np, a_out, ld_a, T))) return rc;
+        if ((rc = dense(e, m, L.g2, m->proj + L.g1_off, Np, g_out, ld_g, T))) return rc;
+    }
     DeltaPrepArgs pa = {};
     pa.q = m->buf[0]; pa.k = m->buf[0] + kd; pa.ld_qk = L.conv_C; pa.G = G; pa.d = d.mm_dim;
-    pa.a = m->buf[1]; pa.ld_a = H * d.mm_dim; pa.A_log = L.st_A_log; pa.dt_bias = L.st_dt_bias; pa.H = H;
+    pa.a = a_out; pa.ld_a = ld_a; pa.A_log = L.st_A_log; pa.dt_bias = L.st_dt_bias; pa.H = H;
     pa.beta = m->proj + L.b_off; pa.ld_b = Np; pa.unit_eps = 1e-6f;
     ColStateArgs cs = {};
     cs.wk = m->buf[0] + kd; cs.ld_wk = L.conv_C; cs.rk = m->buf[0]; cs.ld_rk = L.conv_C;
-    cs.row_decay = m->buf[1]; cs.ld_rd = H * d.mm_dim; cs.val = m->buf[0] + 2 * kd; cs.ld_v = L.conv_C;
+    cs.row_decay = a_out; cs.ld_rd = ld_a; cs.val = m->buf[0] + 2 * kd; cs.ld_v = L.conv_C;
     cs.val_scale = m->proj + L.b_off; cs.ld_vs = Np; cs.H = H; cs.G = G; cs.R = d.mm_dim; cs.P = d.mm_vdim; cs.delta = 1;
     cs.state = L.st_state; cs.y = m->buf[3]; cs.ld_y = vd;
     GroupNormArgs gn = {};
-    gn.x = m->buf[3]; gn.ld_x = vd; gn.gate = m->buf[2]; gn.ld_g = vd; gn.w = L.st_norm; gn.w_gstride = 0; gn.groups = H; gn.n = d.mm_vdim;
+    gn.x = m->buf[3]; gn.ld_x = vd; gn.gate = g_out; gn.ld_g = ld_g; gn.w = L.st_norm; gn.w_gstride = 0; gn.groups = H; gn.n = d.mm_vdim;
     gn.eps = c.norm_eps; gn.gate_first = 0; gn.y = m->buf[3]; gn.ld_y = vd;
     {
         StepProfiler sp(m, st, 4);
@@ -762,7 +780,8 @@ static int ff_relu2(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& 
     return dense(e, m, L.down, m->ff, L.d.n_ff, m->oL, W, T, L.down_b, EPI_BIAS);
 }
 
-static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
+// defer != nullptr: the weighted sum of the expert outputs is left to the caller's residual kernel (described in *defer)
+static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in, MoeJoinArgs* defer) {
     const b2_layer_desc& d = L.d;
     cudaStream_t st = e->stream;
     const int T = r.T, W = m->c.n_embd, slots = d.moe_experts + d.moe_identity, pairs = T * d.moe_top, ff = d.n_ff;
@@ -804,6 +823,11 @@ static int ff_moe(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r,
     DenseArgs dn = {};
     dn.groups = &g2;
     if ((rc = dense(e, m, L.e_down, m->moe_h, ff, m->moe_y, W, pairs, nullptr, EPI_NONE, 1, &dn))) return rc;
+    if (defer) {
+        defer->sel = m->moe_sel; defer->weight = m->moe_weight; defer->pos = tiled ? m->moe_pos : nullptr; defer->rows = m->moe_y; defer->h = in;
+        defer->n_experts = d.moe_experts; defer->top = d.moe_top;
+        return B2_OK;
+    }
     StepProfiler sp(m, st, 7);
     CK(moe_combine_launch(m->moe_sel, m->moe_weight, tiled ? m->moe_pos : nullptr, m->moe_y, in, d.moe_experts, d.moe_top, W, T, m->oL, st));
     e->launches++;
@@ -820,8 +844,8 @@ static int run_mixer(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev&
     }
     return b2_fail(B2_ERR_UNSUPPORTED, "unknown mixer kind");
 }
-static int run_ff(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in) {
-    return L.d.ff_kind == B2_FF_MOE ? ff_moe(e, m, L, r, in) : ff_relu2(e, m, L, r, in);
+static int run_ff(b2_engine* e, LayeredModel* m, LyLayer& L, const RaggedDev& r, const float* in, MoeJoinArgs* defer = nullptr) {
+    return L.d.ff_kind == B2_FF_MOE ? ff_moe(e, m, L, r, in, defer) : ff_relu2(e, m, L, r, in);
 }
 
 static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
@@ -840,12 +864,16 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
         }
     }
     // pre-norm blocks: a branch output waits in m->oL until the next norm (or the end of the layer) adds it to the stream
+    // (a mixture's weighted sum is not even formed before: the same kernel adds it up)
     const float* pending = nullptr;
+    MoeJoinArgs pending_moe = {};
     auto join = [&](const float* norm_w, float* y) -> int {
         StepProfiler sp(m, st, 5);
-        CK(resid_rms_norm_launch(m->x, pending, c.residual_scale, norm_w, 1.f, 1.f, c.norm_eps, W, T, y, st));
+        if (pending_moe.sel) CK(moe_join_launch(pending_moe, m->x, c.residual_scale, norm_w, 1.f, c.norm_eps, W, T, y, st));
+        else CK(resid_rms_norm_launch(m->x, pending, c.residual_scale, norm_w, 1.f, 1.f, c.norm_eps, W, T, y, st));
         e->launches++;
         pending = nullptr;
+        pending_moe = MoeJoinArgs{};
         return B2_OK;
     };
     for (int li = 0; li < c.n_layer; li++) {
@@ -857,8 +885,9 @@ static int run_layers(b2_engine* e, LayeredModel* m, const RaggedDev& r) {
             pending = m->oL;
             if (d.n_ff > 0) {
                 if ((rc = join(L.norm2, m->hn))) return rc;
-                if ((rc = run_ff(e, m, L, r, m->hn))) return rc;
-                pending = m->oL;
+                const bool moe = d.ff_kind == B2_FF_MOE;
+                if ((rc = run_ff(e, m, L, r, m->hn, moe ? &pending_moe : nullptr))) return rc;
+                pending = moe ? nullptr : m->oL;
             }
             if (m->trace || li == c.n_layer - 1) { if ((rc = join(nullptr, nullptr))) return rc; }
         } else {

@@ -236,6 +236,15 @@ cudaError_t moe_sort_launch(const MoeSortArgs& a, cudaStream_t s);
 cudaError_t moe_combine_launch(const int* sel, const float* weight, const int* pos, const float* rows, const float* h, int n_experts,
                                int top, int W, int T, float* out, cudaStream_t s);
 
+// the same sum joined to the residual stream in one pass (pre-norm blocks): x[t] += mult * sum; if (y) y[t] = RMS norm of the
+// new x[t] times (w_offset + w). y may be the buffer h points to (a token's h is read before its y is written).
+struct MoeJoinArgs {
+    const int* sel; const float* weight; const int* pos; const float* rows; const float* h;
+    int n_experts, top;
+};
+cudaError_t moe_join_launch(const MoeJoinArgs& j, float* x, float mult, const float* w, float w_offset, float eps, int W, int T, float* y,
+                            cudaStream_t s);
+
 // ---------------------------------------------------------------- graph (layered.cu)
 struct LayeredModel;
 int layered_finalize(b2_engine* e);

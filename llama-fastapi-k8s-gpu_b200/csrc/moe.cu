@@ -149,4 +149,40 @@ cudaError_t moe_combine_launch(const int* sel, const float* weight, const int* p
     return launch_chain(moe_combine_kernel, dim3(T), dim3(256), 0, s, sel, weight, pos, rows, h, n_experts, top, W, out);
 }
 
+// grid (T): the row lives in shared memory between the sum and the normalisation
+__global__ void __launch_bounds__(256) moe_join_kernel(MoeJoinArgs j, float* __restrict__ x, float mult, const float* __restrict__ w,
+                                                       float w_offset, float eps, int W, float* __restrict__ y) {
+    griddep_launch();
+    griddep_wait();
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const size_t base = (size_t)t * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = 0.f;
+        for (int c = 0; c < j.top; c++) {
+            const int p = t * j.top + c, e = j.sel[p];
+            const float v = e < j.n_experts ? j.rows[(size_t)(j.pos ? j.pos[p] : p) * W + i] : j.h[base + i];
+            acc = fmaf(j.weight[p], v, acc);
+        }
+        const float v = fmaf(mult, acc, x[base + i]);
+        x[base + i] = v;
+        row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!y) return;
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < 8; k++) tot += red[k];
+    const float rinv = 1.f / sqrtf(tot / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) y[base + i] = row[i] * rinv * (w_offset + w[i]);
+}
+cudaError_t moe_join_launch(const MoeJoinArgs& j, float* x, float mult, const float* w, float w_offset, float eps, int W, int T, float* y,
+                            cudaStream_t s) {
+    return launch_chain(moe_join_kernel, dim3(T), dim3(256), (size_t)W * 4, s, j, x, mult, w, w_offset, eps, W, y);
+}
+
 }  // namespace b2
