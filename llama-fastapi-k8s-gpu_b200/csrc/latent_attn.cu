@@ -124,6 +124,104 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(LatentAttnAr
     }
 }
 
+// Even row lengths: a lane holds PAIRS of neighbouring entries (one 4- or 8-byte load per key and 64 entries of the row) and a
+// warp takes four keys per round, so that 4 x E2 loads are in flight per lane before the first dot product is reduced.
+template <bool F32>
+__device__ __forceinline__ float2 row_load2(const void* pool, size_t i) {
+    if constexpr (F32) return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(pool) + i);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(pool) + i);
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+constexpr int LA_KEYS = 4;
+template <int E2, bool F32>
+__global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_pairs_kernel(LatentAttnArgs a, RaggedDev r) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float sm_m[LA_WARPS], sm_l[LA_WARPS];
+    extern __shared__ float sm_o[];                    // [LA_WARPS][rank]
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = r.tok_pos[t];
+    const int* table = a.block_tables[r.seg_slot[r.tok_seg[t]]];
+    const int Dk = a.rank + a.dr;
+    const float* q = a.qv + ((size_t)t * a.H + h) * Dk;
+    float2 qr[E2], acc[E2];
+#pragma unroll
+    for (int e = 0; e < E2; e++) {
+        const int i = 64 * e + 2 * lane;
+        qr[e] = i < Dk ? make_float2(q[i] * a.scale, q[i + 1] * a.scale) : make_float2(0.f, 0.f);
+        acc[e] = make_float2(0.f, 0.f);
+    }
+    const int lo = max(0, pos - a.window + 1);
+    const int n_splits = gridDim.z, n_all = pos - lo + 1, chunk = (n_all + n_splits - 1) / n_splits;
+    const int j_begin = lo + blockIdx.z * chunk, j_end = min(pos + 1, j_begin + chunk);
+    const bool has_sink = warp == 0 && blockIdx.z == 0;
+    float m = has_sink ? a.sink[h] : -INFINITY, l = has_sink ? 1.f : 0.f;
+    for (int j0 = j_begin + warp * LA_KEYS; j0 < j_end; j0 += LA_WARPS * LA_KEYS) {
+        size_t base[LA_KEYS];
+        float2 kv[LA_KEYS][E2];
+        float sc[LA_KEYS];
+#pragma unroll
+        for (int u = 0; u < LA_KEYS; u++) {
+            const int j = min(j0 + u, j_end - 1);          // past the end: the last key again, its weight is dropped below
+            base[u] = ((size_t)table[j / a.block_tokens] * a.block_tokens + j % a.block_tokens) * Dk;
+        }
+#pragma unroll
+        for (int u = 0; u < LA_KEYS; u++)
+#pragma unroll
+            for (int e = 0; e < E2; e++) {
+                const int i = 64 * e + 2 * lane;
+                kv[u][e] = i < Dk ? row_load2<F32>(a.pool, base[u] + i) : make_float2(0.f, 0.f);
+            }
+#pragma unroll
+        for (int u = 0; u < LA_KEYS; u++) {
+            float dot = 0.f;
+#pragma unroll
+            for (int e = 0; e < E2; e++) dot = fmaf(qr[e].x, kv[u][e].x, fmaf(qr[e].y, kv[u][e].y, dot));
+            sc[u] = dot;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < LA_KEYS; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+        float m_new = m;
+#pragma unroll
+        for (int u = 0; u < LA_KEYS; u++) if (j0 + u < j_end) m_new = fmaxf(m_new, sc[u]);
+        const float corr = expf(m - m_new);
+        float p[LA_KEYS], ps = 0.f;
+#pragma unroll
+        for (int u = 0; u < LA_KEYS; u++) { p[u] = j0 + u < j_end ? expf(sc[u] - m_new) : 0.f; ps += p[u]; }
+        l = l * corr + ps;
+#pragma unroll
+        for (int e = 0; e < E2; e++) {
+            float ax = acc[e].x * corr, ay = acc[e].y * corr;
+#pragma unroll
+            for (int u = 0; u < LA_KEYS; u++) { ax = fmaf(p[u], kv[u][e].x, ax); ay = fmaf(p[u], kv[u][e].y, ay); }
+            acc[e] = make_float2(ax, ay);
+        }
+        m = m_new;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < E2; e++) {
+        const int i = 64 * e + 2 * lane;
+        if (i < a.rank) sm_o[warp * a.rank + i] = acc[e].x;
+        if (i + 1 < a.rank) sm_o[warp * a.rank + i + 1] = acc[e].y;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w2 = 0; w2 < LA_WARPS; w2++) M = fmaxf(M, sm_m[w2]);
+    float L = 0.f;
+    for (int w2 = 0; w2 < LA_WARPS; w2++) if (sm_m[w2] > -INFINITY) L += sm_l[w2] * expf(sm_m[w2] - M);
+    float* part = n_splits > 1 ? a.split_scratch + (((size_t)t * a.H + h) * n_splits + blockIdx.z) * (a.rank + 2) : nullptr;
+    if (part && threadIdx.x == 0) { part[0] = M; part[1] = L; }
+    for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
+        float o = 0.f;
+        for (int w2 = 0; w2 < LA_WARPS; w2++) if (sm_m[w2] > -INFINITY) o += sm_o[w2 * a.rank + i] * expf(sm_m[w2] - M);
+        if (part) part[2 + i] = o;
+        else a.o_lat[((size_t)t * a.H + h) * a.rank + i] = o / L;
+    }
+}
+
 // sum of the key ranges of one (token, head) in range order (range 0 carries the sink, so the sum is never empty)
 __global__ void __launch_bounds__(128) latent_merge_kernel(LatentAttnArgs a, int n_splits) {
     griddep_launch();
@@ -315,7 +413,14 @@ cudaError_t latent_attn_launch(const LatentAttnArgs& a, const RaggedDev& r, cuda
     const dim3 grid(r.T, a.H, splits), block(LA_WARPS * 32);
     const size_t smem = (size_t)LA_WARPS * a.rank * 4;
     cudaError_t ce;
-    if (Dk <= 160) ce = launch_chain(latent_attn_kernel<5>, grid, block, smem, s, a, r);
+    if (Dk % 2 == 0) {
+        if (Dk <= 192) ce = a.cache_f32 ? launch_chain(latent_attn_pairs_kernel<3, true>, grid, block, smem, s, a, r)
+                                        : launch_chain(latent_attn_pairs_kernel<3, false>, grid, block, smem, s, a, r);
+        else if (Dk <= 384) ce = a.cache_f32 ? launch_chain(latent_attn_pairs_kernel<6, true>, grid, block, smem, s, a, r)
+                                             : launch_chain(latent_attn_pairs_kernel<6, false>, grid, block, smem, s, a, r);
+        else ce = a.cache_f32 ? launch_chain(latent_attn_pairs_kernel<10, true>, grid, block, smem, s, a, r)
+                              : launch_chain(latent_attn_pairs_kernel<10, false>, grid, block, smem, s, a, r);
+    } else if (Dk <= 160) ce = launch_chain(latent_attn_kernel<5>, grid, block, smem, s, a, r);
     else if (Dk <= 320) ce = launch_chain(latent_attn_kernel<10>, grid, block, smem, s, a, r);
     else ce = launch_chain(latent_attn_kernel<20>, grid, block, smem, s, a, r);
     if (ce != cudaSuccess || splits == 1) return ce;
